@@ -58,6 +58,7 @@ class PageCopy:
 class GroupSpec:
     num_pages: int
     window: int | None = None
+    chunk: int | None = None        # queries read no key in front of their own chunk of this many positions
 
 
 def chain_hash(prev: int | None, tokens) -> int:
@@ -122,7 +123,7 @@ class CacheManager:
             raise ValueError("block_size must be positive")
         self.block_size = block_size
         self.group_specs = groups
-        all_keys = all(g.window is None for g in groups)
+        all_keys = all(g.window is None and g.chunk is None for g in groups)
         self.enable_prefix_caching = bool(enable_prefix_caching and all_keys and num_state_slots == 0)
         self.pools = [PagePool(g.num_pages, self.enable_prefix_caching) for g in groups]
         self._pending_copies: list[PageCopy] = []
@@ -314,14 +315,20 @@ class CacheManager:
 
     def release_behind_window(self, seq: Sequence) -> int:
         """Give back the pages that no later query of `seq` can read: with `c`
-        tokens computed, a window w needs keys from position c - w + 1 on.
+        tokens computed, a window w needs keys from position c - w + 1 on, and a
+        chunked mask of size s those from c - c % s on (the next query sits at c).
         Returns the number of pages released."""
         released = 0
         bs = self.block_size
         for g, spec in enumerate(self.group_specs):
-            if spec.window is None:
+            if spec.window is None and spec.chunk is None:
                 continue
-            first_needed = seq.num_computed_tokens - spec.window + 1
+            c = seq.num_computed_tokens
+            first_needed = 0
+            if spec.window is not None:
+                first_needed = max(first_needed, c - spec.window + 1)
+            if spec.chunk is not None:
+                first_needed = max(first_needed, c - c % spec.chunk)
             table = self._tables(seq)[g]
             j = 0
             while j < len(table) and (j + 1) * bs <= first_needed:

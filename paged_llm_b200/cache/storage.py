@@ -44,7 +44,7 @@ class CacheStorage:
                  num_state_slots: int = 0):
         self.page_size, self.dtype, self.device = page_size, dtype, torch.device(device)
         self.num_pages = num_pages
-        # group paged requirements: same (heads, head_dim, window) -> same group
+        # group paged requirements: same (heads, head_dim, window, chunk) -> same group
         self.group_keys: list[PagedKV] = []
         members: list[list[int]] = []
         for slot in cache_slots:
@@ -82,7 +82,7 @@ class CacheStorage:
         return len(self.group_keys)
 
     def group_specs(self) -> list[GroupSpec]:
-        return [GroupSpec(self.num_pages, key.window) for key in self.group_keys]
+        return [GroupSpec(self.num_pages, key.window, key.chunk) for key in self.group_keys]
 
     def page_bytes(self) -> int:
         """Bytes of one page id across all groups and layers."""

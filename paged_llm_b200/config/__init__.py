@@ -1,8 +1,9 @@
 from .engine import EngineConfig
 from .llama import LlamaConfig, RopeScaling
 from .model import ConfigError, ModelConfig
+from .pomisun import PomisunConfig
 from .registry import ARCHITECTURES, Architecture, parse_model_config, register_architecture, resolve_architecture
 from .sampling import SamplingParams
 
-__all__ = ["EngineConfig", "ConfigError", "LlamaConfig", "ModelConfig", "RopeScaling", "ARCHITECTURES",
+__all__ = ["EngineConfig", "ConfigError", "LlamaConfig", "ModelConfig", "PomisunConfig", "RopeScaling", "ARCHITECTURES",
            "Architecture", "parse_model_config", "register_architecture", "resolve_architecture", "SamplingParams"]

@@ -33,8 +33,11 @@ def register_architecture(name: str, config_class: type, build_spec: Callable) -
 
 
 def resolve_architecture(hf_config: dict) -> Architecture:
-    """The first of config.json's `architectures` that is registered."""
-    names = hf_config.get("architectures") or []
+    """The first of config.json's `architectures` that is registered (a config.json may also give one
+    name under `architecture`)."""
+    names = list(hf_config.get("architectures") or [])
+    if isinstance(hf_config.get("architecture"), str):
+        names.append(hf_config["architecture"])
     for n in names:
         if n in ARCHITECTURES:
             return ARCHITECTURES[n]
@@ -51,6 +54,10 @@ def _register_builtin() -> None:
     from .llama import LlamaConfig
     if "LlamaForCausalLM" not in ARCHITECTURES:
         register_architecture("LlamaForCausalLM", LlamaConfig, llama_spec)
+    from ..models.pomisun import pomisun_spec
+    from .pomisun import PomisunConfig
+    if "Pomisun" not in ARCHITECTURES:
+        register_architecture("Pomisun", PomisunConfig, pomisun_spec)
 
 
 _register_builtin()

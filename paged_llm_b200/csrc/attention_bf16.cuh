@@ -187,13 +187,14 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     };
 
     const int g = lane >> 2, t4 = lane & 3;
-    int pos[2];
+    int pos[2], first[2];
     float slope[2];
     constexpr bool modified = MOD;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int R = it.row_base + wm * 16 + g + 8 * h;
         pos[h] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+        first[h] = attn_first_key(p, max(pos[h], 0));
         slope[h] = MOD && p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             // (rows that pad the tile carry zero queries and are never stored: they need no mask)
             const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0] < 0 ? 0x7fffffff : pos[0],
                                                                         pos[1] < 0 ? 0x7fffffff : pos[1]));
-            const bool full_tile = !modified && p.window <= 0 && kbase + KPW <= hi_cur && kbase + KPW - 1 <= pos_min_warp;
+            const bool full_tile = !modified && p.window <= 0 && p.chunk <= 0 && kbase + KPW <= hi_cur && kbase + KPW - 1 <= pos_min_warp;
             float mx[2] = {-INFINITY, -INFINITY};
             if (full_tile) {
 #pragma unroll
@@ -300,7 +301,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                     for (int e = 0; e < 4; ++e) {
                         const int n = kbase + 8 * j + 2 * t4 + (e & 1);
                         const int pr = pos[e >> 1];
-                        const bool vis = n < hi_cur && n <= pr && (p.window <= 0 || n > pr - p.window);
+                        const bool vis = n < hi_cur && n <= pr && n >= first[e >> 1];
                         const float s = !vis ? -INFINITY
                                         : modified ? attn_score(p, sacc[j][e], slope[e >> 1], n, pr) * LOG2E
                                                    : sacc[j][e] * scale_log2;
@@ -658,6 +659,7 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
     PL_REQUIRE(p.softcap >= 0.f, "attention_bf16: softcap=%f must not be negative", (double)p.softcap);
+    PL_REQUIRE(p.chunk >= 0 && p.window >= 0, "attention_bf16: window=%d, chunk=%d", p.window, p.chunk);
     // Shapes of the decode kernel, by measurement (B200; with so few warps per SM the dependent chain of a
     // warp and the shared memory a block takes decide): head sizes up to 64 walk 128 keys per tile, but 64
     // keys in a ring of three tiles where the work list says that the ranges are long (is_small == 2:
@@ -705,9 +707,9 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
 #if PL_DPAD == 64
     static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
-    if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);
+    if (p.d == 64 && !no_tc && p.chunk <= 0) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);
 #else
-    if (p.d == 128 && !no_tc && tc2::takes(p)) return tc2::launch<128>(p, stream);
+    if (p.d == 128 && !no_tc && p.chunk <= 0 && tc2::takes(p)) return tc2::launch<128>(p, stream);
 #endif
 #endif
     return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64>(p, stream);

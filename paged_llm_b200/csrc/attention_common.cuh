@@ -4,7 +4,8 @@
 // Semantics (xiyiji/paged-llm pagedllm/attention/reference.py:23-55 and
 // triton_kernel.py:22-93): request s has nq new query tokens and a context of Lk
 // keys that includes them; query token i sits at position Lk - nq + i and sees
-// keys 0..position (with a window w: the last w of them); query head h reads kv
+// keys 0..position (with a window w: the last w of them; with a chunk c: those from
+// position - position % c on); query head h reads kv
 // head h / (heads / kv_heads); keys and values are read through the block table.
 #pragma once
 
@@ -40,7 +41,7 @@ __device__ __forceinline__ AttnItem attn_decode_item(const AttnParams& p, int id
     const int last_row = min(it.rows_total, it.row_base + block_rows) - 1;
     const int pos_first = it.lk - it.nq + it.row_base / G;
     const int pos_last = it.lk - it.nq + last_row / G;
-    int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int lo = attn_first_key(p, pos_first);
     int hi = pos_last + 1;
     if (it.splits > 1) {
         int chunk = (hi - lo + it.splits - 1) / it.splits;
@@ -71,7 +72,7 @@ __device__ __forceinline__ AttnItem attn_cluster_item(const AttnParams& p, int s
     it.splits = splits;
     if (it.nq <= 0) return it;
     const int pos_first = it.lk - it.nq;
-    const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo = attn_first_key(p, pos_first);
     const int hi = it.lk;
     int chunk = (hi - lo + splits - 1) / splits;
     chunk = (chunk + 31) / 32 * 32;

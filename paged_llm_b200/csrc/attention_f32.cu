@@ -30,12 +30,13 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
         if (R < it.rows_total) v = q[(size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c];
         Qs[e] = v;
     }
-    int pos[4];
+    int pos[4], first[4];
     float m[4], l[4], acc[4][F32_MAXD / 32], slope[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
         const int R = it.row_base + warp * 4 + rr;
         pos[rr] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+        first[rr] = attn_first_key(p, max(pos[rr], 0));
         slope[rr] = p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
         m[rr] = -INFINITY;
         l[rr] = 0.f;
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
             float s = 0.f;
             for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
             s = attn_score(p, s, slope[rr], n, pos[rr]);
-            const bool vis = n < it.key_hi && n <= pos[rr] && (p.window <= 0 || n > pos[rr] - p.window);
+            const bool vis = n < it.key_hi && n <= pos[rr] && n >= first[rr];
             const float m_new = fmaxf(m[rr], warp_max(vis ? s : -INFINITY));
             if (m_new == -INFINITY) continue;
             const float pj = vis ? expf(s - m_new) : 0.f;
@@ -158,6 +159,7 @@ int pl_attn_check(const AttnParams& p, const char* who) {
     PL_REQUIRE(p.d > 0 && p.d % 16 == 0 && p.d <= 256, "%s: head_dim=%d must be a multiple of 16 up to 256", who, p.d);
     PL_REQUIRE(p.ps > 0, "%s: page_size=%d", who, p.ps);
     PL_REQUIRE(p.window >= 0, "%s: window=%d", who, p.window);
+    PL_REQUIRE(p.chunk >= 0, "%s: chunk=%d", who, p.chunk);
     PL_REQUIRE(p.max_splits >= 1, "%s: max_splits=%d", who, p.max_splits);
     PL_REQUIRE(p.softcap >= 0.f, "%s: softcap=%f must not be negative", who, (double)p.softcap);
     return 0;

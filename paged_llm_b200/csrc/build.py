@@ -39,6 +39,8 @@ MODULES: dict[str, list[str]] = {
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
     # decode attention whose scratch is a static array of the library (see attention_decode_static.h)
     "attn_static": ["common.cu", "attention_decode_static.cu"],
+    # routed experts (router, pairs sorted by expert, grouped products, weighted sum)
+    "moe": ["common.cu", "moe.cu"],
 }
 
 

@@ -38,6 +38,12 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -132,7 +138,18 @@ struct AttnParams {
     // device because a replayed graph sees other lengths).  The first block of the split-context kernels zeroes
     // them, so that no fill kernel stands between two kernels of a layer.  pad_to == 0: nothing to do.
     int pad_seqs, pad_to;
+    // Chunked mask: > 0: positions are cut into chunks of this many, counted from position 0 of the request, and a
+    // query sees only the keys of its own chunk (at or before itself).  0: none.  Combines with `window`.
+    int chunk;
 };
+
+// The lowest key position that the query at `pos` may see (the highest is `pos` itself).
+__device__ __forceinline__ int attn_first_key(const AttnParams& p, int pos) {
+    int lo = 0;
+    if (p.window > 0) lo = max(lo, pos - p.window + 1);
+    if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+    return lo;
+}
 
 // The score of one (query row, key) pair from the raw dot product, in natural-log units.
 __device__ __forceinline__ float attn_score(const AttnParams& p, float dot, float slope, int key_pos, int query_pos) {

@@ -205,7 +205,7 @@ template <> struct Vec16<__nv_bfloat16> {
 };
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int vec) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int vec, int act) {
     const size_t r = blockIdx.y;
     const T* g = gu + r * 2 * I;
     const T* u = g + I;
@@ -218,19 +218,21 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
             Vec16<T>::load(g + c, gv);
             Vec16<T>::load(u + c, uv);
 #pragma unroll
-            for (int i = 0; i < N; ++i) ov[i] = gv[i] / (1.0f + expf(-gv[i])) * uv[i];
+            for (int i = 0; i < N; ++i) ov[i] = (act == 1 ? gelu_tanh_f(gv[i]) : gv[i] / (1.0f + expf(-gv[i]))) * uv[i];
             Vec16<T>::store(o + c, ov);
         }
         return;
     }
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
         const float gg = to_float(g[c]);
-        o[c] = from_float<T>(gg / (1.0f + expf(-gg)) * to_float(u[c]));
+        o[c] = from_float<T>((act == 1 ? gelu_tanh_f(gg) : gg / (1.0f + expf(-gg))) * to_float(u[c]));
     }
 }
 
-PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, int I, cudaStream_t stream) {
+// act: 0 SiLU, 1 the tanh form of GELU.
+PL_EXPORT int pl_act_mul(const void* gate_up, void* out, int dtype, int rows, int I, int act, cudaStream_t stream) {
     if (rows == 0) return 0;
+    PL_REQUIRE(act == 0 || act == 1, "act_mul: unknown activation %d", act);
     PL_REQUIRE(rows > 0 && I > 0 && rows <= 65535 * 16, "silu_mul: bad sizes rows=%d I=%d", rows, I);
     const int per = dtype == PL_F32 ? 4 : 8;
     const int vec = I % per == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0;
@@ -244,14 +246,46 @@ PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, i
         const char* src = (const char*)gate_up + (size_t)r0 * 2 * I * esz;
         char* dst = (char*)out + (size_t)r0 * I * esz;
         if (dtype == PL_F32)
-            silu_mul_kernel<float><<<dim3(bx, nr), threads, 0, stream>>>((const float*)src, (float*)dst, I, vec);
+            silu_mul_kernel<float><<<dim3(bx, nr), threads, 0, stream>>>((const float*)src, (float*)dst, I, vec, act);
         else if (dtype == PL_BF16)
             silu_mul_kernel<__nv_bfloat16><<<dim3(bx, nr), threads, 0, stream>>>((const __nv_bfloat16*)src,
-                                                                                  (__nv_bfloat16*)dst, I, vec);
+                                                                                  (__nv_bfloat16*)dst, I, vec, act);
         else
             return pl_fail("silu_mul: unknown dtype %d", dtype);
         PL_LAUNCHED("silu_mul");
     }
+    return 0;
+}
+
+PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, int I, cudaStream_t stream) {
+    return pl_act_mul(gate_up, out, dtype, rows, I, 0, stream);
+}
+
+// ------------------------------------------------------------------ sums into the residual stream
+// x[i] += branch[i] + extra[i] in float32; branch (float32 or bfloat16) and extra (float32) may each be null.
+template <typename TB>
+__global__ void add_rows_kernel(float* __restrict__ x, const TB* __restrict__ branch, const float* __restrict__ extra,
+                                size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (branch != nullptr) v += to_float(branch[i]);
+        if (extra != nullptr) v += extra[i];
+        x[i] = v;
+    }
+}
+
+PL_EXPORT int pl_add_rows(float* x, const void* branch, int branch_dtype, const float* extra, long long n,
+                          cudaStream_t stream) {
+    if (n == 0) return 0;
+    PL_REQUIRE(n > 0, "add_rows: bad size");
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (branch == nullptr || branch_dtype == PL_F32)
+        add_rows_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)branch, extra, (size_t)n);
+    else if (branch_dtype == PL_BF16)
+        add_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)branch, extra, (size_t)n);
+    else
+        return pl_fail("add_rows: unknown dtype %d", branch_dtype);
+    PL_LAUNCHED("add_rows");
     return 0;
 }
 
@@ -294,19 +328,20 @@ PL_EXPORT int pl_gather_rows(const void* x, const int* idx, void* out, int dtype
 }
 
 // ------------------------------------------------------------------ rotary table
-// table[p][j] = (cos(p * inv_freq[j]), sin(p * inv_freq[j])), angle in float32.
-__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, int P, int half) {
+// table[p][j] = mag * (cos(p * inv_freq[j]), sin(p * inv_freq[j])), angle in float32.
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, int P, int half,
+                                  float mag) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)P * half) return;
     const int p = (int)(i / half), j = (int)(i % half);
     const float ang = (float)p * inv_freq[j];
-    table[i] = make_float2(cosf(ang), sinf(ang));
+    table[i] = make_float2(cosf(ang) * mag, sinf(ang) * mag);
 }
 
-PL_EXPORT int pl_rope_table(const float* inv_freq, float* table, int P, int half, cudaStream_t stream) {
+PL_EXPORT int pl_rope_table(const float* inv_freq, float* table, int P, int half, float mag, cudaStream_t stream) {
     PL_REQUIRE(P > 0 && half > 0, "rope_table: bad sizes P=%d half=%d", P, half);
     const size_t total = (size_t)P * half;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, (float2*)table, P, half);
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, (float2*)table, P, half, mag);
     PL_LAUNCHED("rope_table");
     return 0;
 }
@@ -315,12 +350,13 @@ PL_EXPORT int pl_rope_table(const float* inv_freq, float* table, int P, int half
 // One block per token.  q and k heads of the fused projection row are rotated in
 // place (float32 arithmetic, one rounding), then k and v go to the token's slot:
 // page = block_table[request][pos / page_size], row pos % page_size.
+// v_from_k: the row has no value columns; the values are the keys as projected, before the rotation.
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const float2* __restrict__ table,
                                      int table_len, int rotary_dim, int interleaved, const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                      int bt_stride, T* __restrict__ kv, int num_pages, int nh, int nkv, int d, int ps,
-                                     int write, int vec) {
+                                     int write, int vec, int v_from_k) {
     const int t = blockIdx.x;
     const int s = token_seq[t];
     if (s < 0) return;
@@ -340,7 +376,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
         const int quads_per_head = half / 4;
         const int quads = (nh + nkv) * quads_per_head;
         constexpr int PER = 16 / sizeof(T);
-        const int v_chunks = nkv * (d / PER);
+        const int v_chunks = v_from_k ? 0 : nkv * (d / PER);
         for (int i = threadIdx.x; i < quads + v_chunks; i += blockDim.x) {
             if (i < quads) {
                 const int h = i / quads_per_head, j = (i - h * quads_per_head) * 4;
@@ -358,6 +394,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                     T* dst = kv + ((((size_t)page * 2 + 0) * nkv + (h - nh)) * ps + off) * d;
                     Vec4<T>::store(dst + j, lo);
                     Vec4<T>::store(dst + j + half, hi);
+                    if (v_from_k) {
+                        T* vdst = dst + (size_t)nkv * ps * d;
+                        Vec4<T>::store(vdst + j, a);
+                        Vec4<T>::store(vdst + j + half, b);
+                    }
                 }
             } else if (to_cache) {
                 const int e = i - quads, h = e / (d / PER), c = (e - h * (d / PER)) * PER;
@@ -367,6 +408,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
             }
         }
         return;
+    }
+    if (v_from_k && to_cache) {
+        // the values are the keys as they are now, before the rotation
+        const T* k = row + nh * d;
+        for (int i = threadIdx.x; i < nkv * d; i += blockDim.x) {
+            const int h = i / d, c = i - h * d;
+            kv[((((size_t)page * 2 + 1) * nkv + h) * ps + off) * d + c] = k[i];
+        }
+        __syncthreads();
     }
     if (rotate) {
         const float2* cs = table + (size_t)pos * half;
@@ -411,7 +461,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
             const size_t kdst = ((((size_t)page * 2 + 0) * nkv + h) * ps + off) * d + c;
             const size_t vdst = ((((size_t)page * 2 + 1) * nkv + h) * ps + off) * d + c;
             *reinterpret_cast<uint4*>(kv + kdst) = *reinterpret_cast<const uint4*>(k + h * d + c);
-            *reinterpret_cast<uint4*>(kv + vdst) = *reinterpret_cast<const uint4*>(v + h * d + c);
+            if (!v_from_k) *reinterpret_cast<uint4*>(kv + vdst) = *reinterpret_cast<const uint4*>(v + h * d + c);
         }
         return;
     }
@@ -420,19 +470,19 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
         const size_t kdst = ((((size_t)page * 2 + 0) * nkv + h) * ps + off) * d + c;
         const size_t vdst = ((((size_t)page * 2 + 1) * nkv + h) * ps + off) * d + c;
         kv[kdst] = k[i];
-        kv[vdst] = v[i];
+        if (!v_from_k) kv[vdst] = v[i];
     }
 }
 
 PL_EXPORT int pl_rope_kv_write(void* qkv, int dtype, int T, int row_stride, const float* table, int table_len,
                                int rotary_dim, int interleaved, const int* positions, const int* token_seq,
                                const int* block_table, int bt_stride, void* kv, int num_pages, int nh, int nkv, int d,
-                               int ps, int write, cudaStream_t stream) {
+                               int ps, int write, int v_from_k, cudaStream_t stream) {
     if (T == 0) return 0;
     PL_REQUIRE(T > 0 && nh > 0 && nkv > 0 && d > 0 && ps > 0, "rope_kv_write: bad sizes");
     PL_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0, "rope_kv_write: rotary_dim=%d with d=%d",
                rotary_dim, d);
-    PL_REQUIRE(row_stride >= (nh + 2 * nkv) * d, "rope_kv_write: row stride %d too small", row_stride);
+    PL_REQUIRE(row_stride >= (nh + (v_from_k ? 1 : 2) * nkv) * d, "rope_kv_write: row stride %d too small", row_stride);
     const int threads = 128;
     const int per16 = dtype == PL_F32 ? 4 : 8;
     // 16-byte path: heads, halves and rows start on 16-byte boundaries
@@ -442,11 +492,11 @@ PL_EXPORT int pl_rope_kv_write(void* qkv, int dtype, int T, int row_stride, cons
         rope_kv_write_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, row_stride, (const float2*)table, table_len,
                                                                rotary_dim, interleaved, positions, token_seq,
                                                                block_table, bt_stride, (float*)kv, num_pages, nh, nkv,
-                                                               d, ps, write, vec);
+                                                               d, ps, write, vec, v_from_k);
     else if (dtype == PL_BF16)
         rope_kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
             (__nv_bfloat16*)qkv, row_stride, (const float2*)table, table_len, rotary_dim, interleaved, positions,
-            token_seq, block_table, bt_stride, (__nv_bfloat16*)kv, num_pages, nh, nkv, d, ps, write, vec);
+            token_seq, block_table, bt_stride, (__nv_bfloat16*)kv, num_pages, nh, nkv, d, ps, write, vec, v_from_k);
     else
         return pl_fail("rope_kv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("rope_kv_write");

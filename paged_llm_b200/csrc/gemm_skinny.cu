@@ -44,6 +44,8 @@ struct SkinnyParams {
     int ldx, ldy, M, N, K;
     int num_blocks;              // 16-row blocks of this product
     int I;                       // SiLU: N == 2 * I
+    int act;                     // the gate's activation: 0 SiLU, 1 the tanh form of GELU
+    int v_from_k;                // rotary: no value heads; the values are the keys before the rotation
     // rotary + cache write
     int nh, nkv, d, ps, bt_stride, num_pages, table_len, write;
     const float2* table;         // [positions, d/2] (cos, sin)
@@ -483,14 +485,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
                 if (row_lo >= 0) {
                     const float gate = __bfloat162float(__float2bfloat16_rn(lo));
                     const float up = __bfloat162float(__float2bfloat16_rn(hi));
-                    ((__nv_bfloat16*)p.Y)[(size_t)tok * p.ldy + row_lo] =
-                        __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+                    const float a = p.act == 1 ? gelu_tanh_f(gate) : gate / (1.0f + expf(-gate));
+                    ((__nv_bfloat16*)p.Y)[(size_t)tok * p.ldy + row_lo] = __float2bfloat16_rn(a * up);
                 }
             } else {
                 const int head = row_lo / p.d, i_lo = row_lo - head * p.d, i_hi = i_lo + p.d / 2;
                 float a = __bfloat162float(__float2bfloat16_rn(lo)), b = __bfloat162float(__float2bfloat16_rn(hi));
                 const int s = r_seq[e];
                 const int pos = r_pos[e];
+                const __nv_bfloat16 ua = __float2bfloat16_rn(a), ub = __float2bfloat16_rn(b);      // as projected
                 {
                     const float2 cs = r_cs[e];                  // (1, 0) where nothing is rotated
                     const float ra = a * cs.x - b * cs.y, rb = b * cs.x + a * cs.y;
@@ -510,6 +513,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
                         __nv_bfloat16* dst = p.kv + ((((size_t)page * 2 + sel) * p.nkv + hh) * p.ps + pos % p.ps) * p.d;
                         dst[i_lo] = oa;
                         dst[i_hi] = ob;
+                        if (p.v_from_k) {
+                            __nv_bfloat16* vdst = dst + (size_t)p.nkv * p.ps * p.d;
+                            vdst[i_lo] = ua;
+                            vdst[i_hi] = ub;
+                        }
                     }
                 }
             }
@@ -641,9 +649,11 @@ PL_EXPORT int pl_gemm_skinny_add(const void* X, int ldx, const void* W, float* r
 
 // Y[M, I] = silu(X Wg^T) * (X Wu^T), W = [Wg; Wu] of shape [2I, K].
 PL_EXPORT int pl_gemm_skinny_silu(const void* X, int ldx, const void* W, void* Y, int ldy, int M, int I, int K,
-                                  const float* part_in, const void* norm_w, int norm_w_dtype, float eps,
+                                  const float* part_in, const void* norm_w, int norm_w_dtype, float eps, int act,
                                   cudaStream_t stream) {
     SkinnyParams p = {};
+    PL_REQUIRE(act == 0 || act == 1, "gemm_skinny_silu: unknown activation %d", act);
+    p.act = act;
     p.X = X;
     p.W = (const __nv_bfloat16*)W;
     p.Y = Y;
@@ -661,12 +671,13 @@ PL_EXPORT int pl_gemm_skinny_silu(const void* X, int ldx, const void* W, void* Y
 }
 
 // Y[M, (nh + 2 nkv) d] = X W^T with q and k heads rotated (pairs i, i + d/2 over the whole
-// head) and k, v written to their cache slots.
+// head) and k, v written to their cache slots.  v_from_k: W has no value rows, Y is [M, (nh + nkv) d],
+// and the value written beside a key is that key as projected, before the rotation.
 PL_EXPORT int pl_gemm_skinny_rope(const void* X, int ldx, const void* W, void* Y, int ldy, int M, int K, int nh,
                                   int nkv, int d, const float* table, int table_len, const int* positions,
                                   const int* token_seq, const int* block_table, int bt_stride, void* kv,
                                   int num_pages, int ps, int write, const float* part_in, const void* norm_w,
-                                  int norm_w_dtype, float eps, cudaStream_t stream) {
+                                  int norm_w_dtype, float eps, int v_from_k, cudaStream_t stream) {
     SkinnyParams p = {};
     p.X = X;
     p.W = (const __nv_bfloat16*)W;
@@ -674,7 +685,8 @@ PL_EXPORT int pl_gemm_skinny_rope(const void* X, int ldx, const void* W, void* Y
     p.ldx = ldx;
     p.ldy = ldy;
     p.M = M;
-    p.N = (nh + 2 * nkv) * d;
+    p.N = (nh + (v_from_k ? 1 : 2) * nkv) * d;
+    p.v_from_k = v_from_k ? 1 : 0;
     p.K = K;
     p.nh = nh;
     p.nkv = nkv;
@@ -689,7 +701,7 @@ PL_EXPORT int pl_gemm_skinny_rope(const void* X, int ldx, const void* W, void* Y
     p.token_seq = token_seq;
     p.block_table = block_table;
     p.kv = (__nv_bfloat16*)kv;
-    p.num_blocks = (nh + 2 * nkv) * (d / 16);
+    p.num_blocks = (nh + (v_from_k ? 1 : 2) * nkv) * (d / 16);
     set_norm(p, part_in, norm_w, norm_w_dtype, eps);
     if (int rc = check_common(p, "gemm_skinny_rope")) return rc;
     PL_REQUIRE(d % 16 == 0 && d > 0 && nh > 0 && nkv > 0 && ps > 0, "gemm_skinny_rope: bad head sizes");

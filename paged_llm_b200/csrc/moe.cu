@@ -1,0 +1,423 @@
+// A feed-forward of routed experts: router, the list of (token, expert) pairs sorted by expert, the
+// experts' products over that list, and the weighted sum.
+//
+//   z = W_r h (float32);  the k largest z choose the experts;  their weights are the softmax over those k;
+//   y = sum_j weight_j * down_e(j)(act(gate_e(j) h) * up_e(j) h)  [+ sigmoid(w_s . h) * shared(h)]
+//
+// Nothing here looks at the batch on the host: the counts per expert stay on the device, every kernel is
+// launched for the most tiles the step can have and blocks beyond the real count leave at once, so a step
+// can be captured and replayed.  A pair is (token t, choice j), numbered t * k + j; tiles of BM pairs of one
+// expert are listed in `sorted` (padded per expert with -1) and `tile_expert`.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float act_f(int act, float z) { return act == 1 ? gelu_tanh_f(z) : silu_f(z); }
+
+// ------------------------------------------------------------------ router
+// One warp per token.  logits[e] = sum_c h[c] * W[e][c] in float32 for the E experts and, if `shared_gate`,
+// one more row of W whose sigmoid is the token's factor for the shared expert.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ W,
+                                                        int tokens, int D, int E, int k, int shared_gate,
+                                                        int* __restrict__ top_idx, float* __restrict__ top_w,
+                                                        float* __restrict__ gate) {
+    extern __shared__ float z_all[];                    // [4][E + 1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    float* z = z_all + warp * (E + 1);
+    const T* x = h + (size_t)t * ldh;
+    const int rows = E + (shared_gate ? 1 : 0);
+    for (int e = 0; e < rows; ++e) {
+        const T* w = W + (size_t)e * D;
+        float s = 0.f;
+        for (int c = lane; c < D; c += 32) s = fmaf(to_float(x[c]), to_float(w[c]), s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s;
+    }
+    __syncwarp();
+    if (shared_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
+    // the k largest, one after the other; among equals the lowest index
+    float chosen_z = 0.f, z_max = 0.f, sum = 0.f;
+    int chosen_e = -1;                                  // lane j keeps choice j (k <= 32)
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < arg)) {
+                best = v;
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        if (arg >= E) arg = 0;                          // (only if every logit is NaN)
+        if (j == 0) z_max = best;
+        if (lane == j) {
+            chosen_z = best;
+            chosen_e = arg;
+        }
+        __syncwarp();
+        if (lane == 0) z[arg] = -INFINITY;
+        __syncwarp();
+    }
+    const float pj = lane < k ? expf(chosen_z - z_max) : 0.f;
+    sum = warp_sum(pj);
+    if (lane < k) {
+        top_idx[(size_t)t * k + lane] = chosen_e;
+        top_w[(size_t)t * k + lane] = pj / sum;
+    }
+}
+
+// ------------------------------------------------------------------ pairs sorted by expert
+// One block.  sorted[cap]: the pairs of expert 0, padded with -1 to a multiple of BM, then those of expert
+// 1, ...; tile_expert[i]: the expert of tile i; *n_tiles: the tiles in use.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ top_idx, int n_pairs, int E, int BM,
+                                                         int cap, int* __restrict__ sorted, int* __restrict__ tile_expert,
+                                                         int* __restrict__ n_tiles) {
+    __shared__ int cnt[1024], off[1025];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+    for (int i = tid; i < cap; i += blockDim.x) sorted[i] = -1;
+    __syncthreads();
+    for (int i = tid; i < n_pairs; i += blockDim.x) {
+        const int e = top_idx[i];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = run;
+            run += (cnt[e] + BM - 1) / BM * BM;
+        }
+        off[E] = run;
+        *n_tiles = run / BM;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+        for (int i = off[e] / BM; i < off[e + 1] / BM; ++i) tile_expert[i] = e;
+        cnt[e] = 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_pairs; i += blockDim.x) {
+        const int e = top_idx[i];
+        if (e >= 0 && e < E) {
+            const int at = off[e] + atomicAdd(&cnt[e], 1);
+            if (at < cap) sorted[at] = i;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ the experts' products
+struct MoeGemm {
+    const void* A;              // rows of the left operand; pair i reads row i / a_div
+    const void* W;              // [E][rows_w][K]: rows_w = 2 N (gate rows, then up rows) if gated, else N
+    void* out;                  // gated: [pairs][ldo] in the compute type; else float32 [pairs][ldo]
+    const int* sorted;
+    const int* tile_expert;
+    const int* n_tiles;
+    const float* row_scale;     // [pairs] or null: the result of pair i is multiplied by it
+    int lda, a_div, ldo, n_pairs, N, K, act;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int MG_BN = 64, MG_BK = 64, MG_PITCH = MG_BK + 8, MG_STAGES = 3;
+
+template <int BM, bool GATED>
+constexpr int moe_gemm_smem() { return MG_STAGES * (BM + (GATED ? 2 : 1) * MG_BN) * MG_PITCH * 2; }
+
+// bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulation).  grid: (tiles, ceil(N / 64)); a
+// block takes BM pairs of one expert and 64 columns (gated: 64 gate and the 64 matching up columns);
+// operands come in through a ring of three cp.async stages of 64 k each, zero-filled outside the matrices.
+// BM = 64: four warps of 16 rows; BM = 16 (few pairs per expert: decoding): four warps of 16 columns.
+template <int BM, bool GATED>
+__global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(MoeGemm p) {
+    constexpr int BN = MG_BN, BK = MG_BK, PITCH = MG_PITCH, STAGES = MG_STAGES;
+    constexpr int NB = GATED ? 2 : 1;
+    constexpr int WM = BM / 16, WNW = 4 / WM, WN = BN / WNW, NF = WN / 8;
+    const int tile = blockIdx.x;
+    if (tile >= *p.n_tiles) return;
+    const int e = p.tile_expert[tile], n0 = blockIdx.y * BN;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [STAGES][BM][PITCH]
+    __nv_bfloat16* Bs = As + STAGES * BM * PITCH;                             // [STAGES][NB * BN][PITCH]
+    __shared__ int rows[BM];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < BM) {
+        const int id = p.sorted[(size_t)tile * BM + tid];
+        rows[tid] = id >= 0 && id < p.n_pairs ? id : -1;
+    }
+    __syncthreads();
+    const __nv_bfloat16* A = (const __nv_bfloat16*)p.A;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + (size_t)e * NB * p.N * p.K;
+    constexpr int CH = BK / 8;
+    auto load_stage = [&](int stage, int k0) {
+        __nv_bfloat16* as = As + stage * BM * PITCH;
+        __nv_bfloat16* bs = Bs + stage * NB * BN * PITCH;
+        for (int i = tid; i < BM * CH; i += 128) {
+            const int r = i / CH, c = i - r * CH, kk = k0 + c * 8;
+            const bool ok = rows[r] >= 0 && kk < p.K;
+            const __nv_bfloat16* src = ok ? A + (size_t)(rows[r] / p.a_div) * p.lda + kk : A;
+            cp_async16(as + r * PITCH + c * 8, src, ok ? 16 : 0);
+        }
+        for (int i = tid; i < NB * BN * CH; i += 128) {
+            const int r = i / CH, c = i - r * CH, kk = k0 + c * 8;
+            const int which = r / BN, n = n0 + r % BN;
+            const bool ok = n < p.N && kk < p.K;
+            const __nv_bfloat16* src = ok ? W + ((size_t)which * p.N + n) * p.K + kk : W;
+            cp_async16(bs + r * PITCH + c * 8, src, ok ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    float acc[NB][NF][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int j = 0; j < NF; ++j)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[b][j][q] = 0.f;
+    const int wm = warp % WM, wn = warp / WM;
+    const int nk = (p.K + BK - 1) / BK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < nk) load_stage(s, s * BK);
+        else cp_async_commit();
+    }
+    for (int kt = 0; kt < nk; ++kt) {
+        if (kt + STAGES - 1 < nk) load_stage((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
+        else cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        const __nv_bfloat16* as = As + (kt % STAGES) * BM * PITCH;
+        const __nv_bfloat16* bs = Bs + (kt % STAGES) * NB * BN * PITCH;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+            uint32_t a[4];
+            ldmatrix_x4(a, as + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int n2 = 0; n2 < WN / 16; ++n2) {
+                    uint32_t f[4];
+                    ldmatrix_x4(f, bs + (b * BN + wn * WN + n2 * 16 + (lane & 7) + (lane >> 4) * 8) * PITCH + kk * 16 +
+                                       ((lane >> 3) & 1) * 8);
+                    mma_bf16(acc[b][2 * n2], a, f[0], f[1]);
+                    mma_bf16(acc[b][2 * n2 + 1], a, f[2], f[3]);
+                }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int id = rows[wm * 16 + g + 8 * hh];
+        if (id < 0) continue;
+        const float sc = !GATED && p.row_scale != nullptr ? p.row_scale[id] : 1.f;
+#pragma unroll
+        for (int j = 0; j < NF; ++j)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int col = n0 + wn * WN + 8 * j + 2 * t4 + q;
+                if (col >= p.N) continue;
+                if (GATED) {
+                    const float v = act_f(p.act, acc[0][j][2 * hh + q]) * acc[NB - 1][j][2 * hh + q];
+                    ((__nv_bfloat16*)p.out)[(size_t)id * p.ldo + col] = __float2bfloat16_rn(v);
+                } else {
+                    ((float*)p.out)[(size_t)id * p.ldo + col] = acc[0][j][2 * hh + q] * sc;
+                }
+            }
+    }
+}
+
+// The same on the CUDA cores with one FFMA chain per result in k order, for float32 (true 32-bit) and for
+// bfloat16 sizes that the tensor-core form does not take.  Tiles of 16 pairs x 64 columns, 256 threads,
+// four columns each.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256) moe_gemm_plain_kernel(MoeGemm p) {
+    constexpr int BM = 16, BN = 64, BK = 32, NB = GATED ? 2 : 1;
+    const int tile = blockIdx.x;
+    if (tile >= *p.n_tiles) return;
+    const int e = p.tile_expert[tile], n0 = blockIdx.y * BN;
+    __shared__ float As[BM][BK + 1];
+    __shared__ float Bs[NB][BK][BN + 1];
+    __shared__ int rows[BM];
+    const int tid = threadIdx.x;
+    if (tid < BM) {
+        const int id = p.sorted[(size_t)tile * BM + tid];
+        rows[tid] = id >= 0 && id < p.n_pairs ? id : -1;
+    }
+    __syncthreads();
+    const T* A = (const T*)p.A;
+    const T* W = (const T*)p.W + (size_t)e * NB * p.N * p.K;
+    const int r = tid / 16, c4 = (tid % 16) * 4;
+    float acc[NB][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[b][j] = 0.f;
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+        for (int i = tid; i < BM * BK; i += 256) {
+            const int rr = i / BK, kk = i - rr * BK;
+            As[rr][kk] = rows[rr] >= 0 && k0 + kk < p.K ? to_float(A[(size_t)(rows[rr] / p.a_div) * p.lda + k0 + kk]) : 0.f;
+        }
+        for (int i = tid; i < NB * BN * BK; i += 256) {
+            const int which = i / (BN * BK), rem = i - which * BN * BK, n = rem / BK, kk = rem - n * BK;
+            Bs[which][kk][n] = n0 + n < p.N && k0 + kk < p.K ? to_float(W[((size_t)which * p.N + n0 + n) * p.K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < BK; ++kk) {
+            const float a = As[r][kk];
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[b][j] = fmaf(a, Bs[b][kk][c4 + j], acc[b][j]);
+        }
+        __syncthreads();
+    }
+    const int id = rows[r];
+    if (id < 0) return;
+    const float sc = !GATED && p.row_scale != nullptr ? p.row_scale[id] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int col = n0 + c4 + j;
+        if (col >= p.N) continue;
+        if (GATED) ((T*)p.out)[(size_t)id * p.ldo + col] = from_float<T>(act_f(p.act, acc[0][j]) * acc[NB - 1][j]);
+        else ((float*)p.out)[(size_t)id * p.ldo + col] = acc[0][j] * sc;
+    }
+}
+
+// y[t] = sum_j pair_out[t * k + j]  (+ gate[t] * shared[t]), float32.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, int k, const T* __restrict__ shared,
+                                   const float* __restrict__ gate, float* __restrict__ y, int D) {
+    const size_t t = blockIdx.x;
+    const float gt = shared != nullptr ? gate[t] : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < k; ++j) s += pair_out[(t * k + j) * D + c];
+        if (shared != nullptr) s = fmaf(gt, to_float(shared[t * D + c]), s);
+        y[t * D + c] = s;
+    }
+}
+
+template <int BM, bool GATED>
+int launch_moe_bf16(const MoeGemm& p, int max_tiles, cudaStream_t stream) {
+    auto kernel = moe_gemm_bf16_kernel<BM, GATED>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    PL_CUDA(cudaGetDevice(&dev));
+    PL_REQUIRE(dev >= 0 && dev < 64, "moe_gemm: device index %d is out of range", dev);
+    if (!attr_set[dev]) {
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_gemm_smem<BM, GATED>()));
+        attr_set[dev] = true;
+    }
+    kernel<<<dim3(max_tiles, (p.N + MG_BN - 1) / MG_BN), 128, moe_gemm_smem<BM, GATED>(), stream>>>(p);
+    PL_LAUNCHED("moe_gemm_bf16");
+    return 0;
+}
+
+}  // namespace
+
+PL_EXPORT int pl_moe_route(const void* h, int ldh, const void* W, int dtype, int tokens, int D, int E, int k,
+                           int shared_gate, int* top_idx, float* top_w, float* gate, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    PL_REQUIRE(tokens > 0 && D > 0 && E > 0 && k > 0 && k <= E && k <= 32 && E <= 1024,
+               "moe_route: tokens=%d width=%d experts=%d top=%d (top <= 32, experts <= 1024)", tokens, D, E, k);
+    const size_t smem = (size_t)4 * (E + 1) * sizeof(float);
+    const dim3 grid((tokens + 3) / 4);
+    if (dtype == PL_F32)
+        moe_route_kernel<float><<<grid, 128, smem, stream>>>((const float*)h, ldh, (const float*)W, tokens, D, E, k,
+                                                              shared_gate, top_idx, top_w, gate);
+    else if (dtype == PL_BF16)
+        moe_route_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)W,
+                                                                      tokens, D, E, k, shared_gate, top_idx, top_w, gate);
+    else
+        return pl_fail("moe_route: unknown dtype %d", dtype);
+    PL_LAUNCHED("moe_route");
+    return 0;
+}
+
+PL_EXPORT int pl_moe_align(const int* top_idx, int n_pairs, int E, int BM, int cap, int* sorted, int* tile_expert,
+                           int* n_tiles, cudaStream_t stream) {
+    PL_REQUIRE(n_pairs > 0 && E > 0 && E <= 1024 && (BM == 16 || BM == 64) && cap % BM == 0,
+               "moe_align: pairs=%d experts=%d BM=%d cap=%d", n_pairs, E, BM, cap);
+    moe_align_kernel<<<1, 1024, 0, stream>>>(top_idx, n_pairs, E, BM, cap, sorted, tile_expert, n_tiles);
+    PL_LAUNCHED("moe_align");
+    return 0;
+}
+
+// gated != 0: out[pair][N] = act(A W_gate^T) * (A W_up^T) in `dtype`; else out[pair][N] = (A W^T) * row_scale in float32.
+// BM is the tile height `sorted` was made for; tensor_cores != 0 asks for the mma.sync form (bfloat16, K % 8 == 0,
+// lda % 8 == 0), which takes BM 16 or 64; the plain form takes BM 16 only.
+PL_EXPORT int pl_moe_gemm(const void* A, int lda, int a_div, const void* W, void* out, int ldo, const int* sorted,
+                          const int* tile_expert, const int* n_tiles, const float* row_scale, int n_pairs, int N, int K,
+                          int gated, int act, int dtype, int BM, int max_tiles, int tensor_cores, cudaStream_t stream) {
+    PL_REQUIRE(n_pairs > 0 && N > 0 && K > 0 && a_div > 0 && max_tiles > 0, "moe_gemm: bad sizes");
+    PL_REQUIRE(act == 0 || act == 1, "moe_gemm: unknown activation %d", act);
+    MoeGemm p = {A, W, out, sorted, tile_expert, n_tiles, row_scale, lda, a_div, ldo, n_pairs, N, K, act};
+    if (tensor_cores) {
+        PL_REQUIRE(dtype == PL_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
+                   "moe_gemm: the tensor-core form takes bfloat16 with K and lda multiples of 8");
+        if (BM == 64) return gated ? launch_moe_bf16<64, true>(p, max_tiles, stream) : launch_moe_bf16<64, false>(p, max_tiles, stream);
+        if (BM == 16) return gated ? launch_moe_bf16<16, true>(p, max_tiles, stream) : launch_moe_bf16<16, false>(p, max_tiles, stream);
+        return pl_fail("moe_gemm: BM=%d", BM);
+    }
+    PL_REQUIRE(BM == 16, "moe_gemm: the plain form takes tiles of 16 pairs, not %d", BM);
+    const dim3 grid(max_tiles, (N + 63) / 64);
+    if (dtype == PL_F32) {
+        if (gated) moe_gemm_plain_kernel<float, true><<<grid, 256, 0, stream>>>(p);
+        else moe_gemm_plain_kernel<float, false><<<grid, 256, 0, stream>>>(p);
+    } else if (dtype == PL_BF16) {
+        if (gated) moe_gemm_plain_kernel<__nv_bfloat16, true><<<grid, 256, 0, stream>>>(p);
+        else moe_gemm_plain_kernel<__nv_bfloat16, false><<<grid, 256, 0, stream>>>(p);
+    } else {
+        return pl_fail("moe_gemm: unknown dtype %d", dtype);
+    }
+    PL_LAUNCHED("moe_gemm_plain");
+    return 0;
+}
+
+PL_EXPORT int pl_moe_combine(const float* pair_out, int k, const void* shared, int shared_dtype, const float* gate,
+                             float* y, int tokens, int D, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    PL_REQUIRE(tokens > 0 && D > 0 && k > 0, "moe_combine: bad sizes");
+    const int threads = D >= 1024 ? 256 : 128;
+    if (shared == nullptr || shared_dtype == PL_F32)
+        moe_combine_kernel<float><<<tokens, threads, 0, stream>>>(pair_out, k, (const float*)shared, gate, y, D);
+    else if (shared_dtype == PL_BF16)
+        moe_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(pair_out, k, (const __nv_bfloat16*)shared, gate, y, D);
+    else
+        return pl_fail("moe_combine: unknown dtype %d", shared_dtype);
+    PL_LAUNCHED("moe_combine");
+    return 0;
+}

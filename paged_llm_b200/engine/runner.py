@@ -360,7 +360,8 @@ class ModelRunner:
             classify = getattr(self.ops, "long_context_class", None)
             if classify is not None and self.plan_keys:
                 longest = max(it.seq.num_computed_tokens for it in items) + 1
-                classes = tuple(bool(not key[2] and classify(bucket, key[1], longest)) for key in self.plan_keys)
+                classes = tuple(bool(not key[2] and not any(key[4:]) and classify(bucket, key[1], longest))
+                                for key in self.plan_keys)
                 if any(classes):
                     return ("decode", bucket, classes)
             return ("decode", bucket)
@@ -482,7 +483,7 @@ class ModelRunner:
                     buf[o + len(row):o + stride] = 0
         # the work lists change only when a context grows past another multiple of the split size
         step_keys = getattr(self.ops, "MIN_SPLIT_KEYS", 128)
-        windowed = any(key[2] for key in self.plan_keys)
+        windowed = any(key[2] or any(key[4:]) for key in self.plan_keys)
         tag = None if windowed else tuple(-(-k // step_keys) for k in klen)
         if tag is None or tag != entry.plan_tag:
             entry.plan_tag = tag

@@ -45,8 +45,18 @@ class AttnParams(ctypes.Structure):
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
         ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
         ("softcap", c_float), ("slopes", c_void_p), ("rope_table", c_void_p), ("rope_len", c_int),
-        ("pad_seqs", c_int), ("pad_to", c_int),
+        ("pad_seqs", c_int), ("pad_to", c_int), ("chunk", c_int),
     ]
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}       # codes of the gate's activation in the kernels
+
+
+def attention_plan_key(num_heads: int, num_kv_heads: int, window, head_dim: int, chunk=None) -> tuple:
+    """What a step's attention work lists depend on: (query heads per kv head, kv heads, window, head size) and,
+    for a chunked mask, the chunk."""
+    key = (num_heads // num_kv_heads, num_kv_heads, window, head_dim)
+    return key + (chunk,) if chunk else key
 
 
 _LIBS: dict[str, ctypes.CDLL] = {}
@@ -228,13 +238,31 @@ class CudaOps:
         return y
 
     def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+        return self.act_mul(gate_up, "silu")
+
+    def act_mul(self, gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """act(gate) * up for rows [gate | up]; the activation is "silu" or "gelu_tanh", in float32 inside."""
         rows, two_i = gate_up.shape
         assert gate_up.is_contiguous() and two_i % 2 == 0
         out = torch.empty((rows, two_i // 2), dtype=gate_up.dtype, device=self.device)
-        _check(self.core, self.core.pl_silu_mul(self._p(gate_up), self._p(out), self._code(gate_up), rows, two_i // 2,
-                                                self._stream))
+        _check(self.core, self.core.pl_act_mul(self._p(gate_up), self._p(out), self._code(gate_up), rows, two_i // 2,
+                                               ACTIVATIONS[activation], self._stream))
         self.launches += 1
         return out
+
+    def add_rows(self, x: torch.Tensor, branch=None, extra: torch.Tensor | None = None) -> torch.Tensor:
+        """x += branch + extra in place, in float32 (x is the residual stream; either addend may be None)."""
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        if branch is not None:
+            assert branch.shape == x.shape and branch.is_contiguous()
+        if extra is not None:
+            assert extra.shape == x.shape and extra.is_contiguous() and extra.dtype == torch.float32
+        if branch is None and extra is None:
+            return x
+        _check(self.core, self.core.pl_add_rows(self._p(x), self._p(branch), self._code(branch) if branch is not None else PL_F32,
+                                                self._p(extra), c_longlong(x.numel()), self._stream))
+        self.launches += 1
+        return x
 
     def gather_rows(self, x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         n, H = idx.numel(), x.shape[1]
@@ -331,7 +359,10 @@ class CudaOps:
         return self.add_rms_norm(x, self.linear(h, w), norm_w, eps)
 
     def gated_silu_linear(self, h, w_gate_up: torch.Tensor) -> torch.Tensor:
-        """silu(h Wg^T) * (h Wu^T) for W = [Wg; Wu]: one kernel for few tokens, else the
+        return self.gated_act_linear(h, w_gate_up, "silu")
+
+    def gated_act_linear(self, h, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+        """act(h Wg^T) * (h Wu^T) for W = [Wg; Wu]: one kernel for few tokens, else the
         product followed by the activation kernel."""
         M, K = h.shape
         I = w_gate_up.shape[0] // 2
@@ -339,27 +370,32 @@ class CudaOps:
             x, ldx, part, nw, nwc, eps = self._norm_args(h)
             out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
             _check(self.core, self.core.pl_gemm_skinny_silu(x, ldx, self._p(w_gate_up), self._p(out), I, M, I, K,
-                                                            part, nw, nwc, eps, self._stream))
+                                                            part, nw, nwc, eps, ACTIVATIONS[activation], self._stream))
             self.launches += 1
             return out
         h = self.materialize(h)
-        if self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
+        if activation == "silu" and self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
             out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
             self._gemm_tc(h, w_gate_up, out, None, I, 2)
             return out
-        return self.silu_mul(self.linear(h, w_gate_up))
+        return self.act_mul(self.linear(h, w_gate_up), activation)
 
-    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True) -> torch.Tensor:
+    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True,
+                       value_from_key=False) -> torch.Tensor:
         """The fused q/k/v projection with rotary positions applied to q and k and k, v
         written to the cache.  Returns the [T, (nh + 2 nkv) d] buffer whose first nh*d
-        columns are the rotated queries."""
+        columns are the rotated queries.  `value_from_key`: there is no value projection (w_qkv
+        stacks q and k only, the buffer is [T, (nh + nkv) d]) and the value written beside a key
+        is that key as projected, before its rotation."""
         M, K = h.shape
-        N = (nh + 2 * nkv) * d
+        N = (nh + (1 if value_from_key else 2) * nkv) * d
+        assert w_qkv.shape[0] == N
         fusable = (self._skinny_ok(h, N) and position is not None and position.pairing == "half"
                    and position.rotary_dim == d and M == ctx.num_tokens)
         if not fusable:
             qkv = self.linear(h, w_qkv)
-            self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+            self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write,
+                               value_from_key=value_from_key)
             return qkv
         x, ldx, part, nw, nwc, eps = self._norm_args(h)
         qkv = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
@@ -368,20 +404,76 @@ class CudaOps:
             x, ldx, self._p(w_qkv), self._p(qkv), N, M, K, nh, nkv, d, self._p(position.table),
             position.table.shape[0], self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table),
             block_table.shape[1], self._p(kv), kv.shape[0], kv.shape[3], 1 if write else 0, part, nw, nwc, eps,
-            self._stream))
+            1 if value_from_key else 0, self._stream))
         self.launches += 1
         return qkv
 
+    # ---- routed experts ----------------------------------------------------------
+    def routed_experts(self, h, w_router, w_gate_up, w_down, top_k: int, activation: str = "silu", shared=None,
+                       shared_activation: str = "silu") -> torch.Tensor:
+        """The feed-forward of routed experts for the step's tokens: float32 [T, D].
+
+        w_router [E (+1), D]: the router's rows and, with a shared expert, the row of its gate; w_gate_up
+        [E, 2F, D] (gate rows over up rows) and w_down [E, D, F]; `shared` = (gate over up [2Fs, D], down
+        [D, Fs]) or None.  Router logits, top-k, the softmax over the chosen logits and the final weighted
+        sum are float32.  Kernels: router; (token, choice) pairs sorted by expert on the device; the
+        experts' two products over tiles of that list (bfloat16: mma.sync tiles of 64 pairs, or of 16 when
+        experts get few pairs as in decoding; float32 and odd sizes: FFMA chains in k order); the sum.
+        Nothing is read back, so the step can be captured."""
+        h = self.materialize(h)
+        assert h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_router.is_contiguous()
+        T, D = h.shape
+        E, F2, _ = w_gate_up.shape
+        F = F2 // 2
+        assert w_down.shape == (E, D, F) and w_router.shape == (E + (1 if shared is not None else 0), D)
+        assert w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype and w_router.dtype == h.dtype
+        lib = load_module("moe")
+        dev, code = self.device, self._code(h)
+        pairs = T * top_k
+        top_idx = torch.empty(pairs, dtype=torch.int32, device=dev)
+        top_w = torch.empty(pairs, dtype=torch.float32, device=dev)
+        gate = torch.empty(T, dtype=torch.float32, device=dev) if shared is not None else None
+        _check(lib, lib.pl_moe_route(self._p(h), D, self._p(w_router), code, T, D, E, top_k, 1 if shared is not None else 0,
+                                     self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
+        tensor_cores = h.dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
+        BM = 64 if tensor_cores and pairs >= 32 * E else 16
+        max_tiles = pairs // BM + min(pairs, E)
+        sorted_pairs = torch.empty(max_tiles * BM, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        _check(lib, lib.pl_moe_align(self._p(top_idx), pairs, E, BM, max_tiles * BM, self._p(sorted_pairs),
+                                     self._p(tile_expert), self._p(n_tiles), self._stream))
+        inter = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        act = ACTIVATIONS[activation]
+        _check(lib, lib.pl_moe_gemm(self._p(h), D, top_k, self._p(w_gate_up), self._p(inter), F, self._p(sorted_pairs),
+                                    self._p(tile_expert), self._p(n_tiles), c_void_p(0), pairs, F, D, 1, act, code, BM,
+                                    max_tiles, 1 if tensor_cores else 0, self._stream))
+        pair_out = torch.empty((pairs, D), dtype=torch.float32, device=dev)
+        _check(lib, lib.pl_moe_gemm(self._p(inter), F, 1, self._p(w_down), self._p(pair_out), D, self._p(sorted_pairs),
+                                    self._p(tile_expert), self._p(n_tiles), self._p(top_w), pairs, D, F, 0, act, code, BM,
+                                    max_tiles, 1 if tensor_cores else 0, self._stream))
+        self.launches += 4
+        s = None
+        if shared is not None:
+            s = self.linear(self.gated_act_linear(h, shared[0], shared_activation), shared[1])
+        y = torch.empty((T, D), dtype=torch.float32, device=dev)
+        _check(lib, lib.pl_moe_combine(self._p(pair_out), top_k, self._p(s), self._code(s) if s is not None else PL_F32,
+                                       self._p(gate), self._p(y), T, D, self._stream))
+        self.launches += 1
+        return y
+
     # ---- positions ---------------------------------------------------------------
-    def rope_table(self, inv_freq: torch.Tensor, max_positions: int) -> torch.Tensor:
+    def rope_table(self, inv_freq: torch.Tensor, max_positions: int, magnitude: float = 1.0) -> torch.Tensor:
+        """[positions, pairs, 2] float32: (cos, sin) of position * inv_freq, both times `magnitude`."""
         inv_freq = inv_freq.to(device=self.device, dtype=torch.float32).contiguous()
         half = inv_freq.numel()
         table = torch.empty((max_positions, half, 2), dtype=torch.float32, device=self.device)
-        _check(self.core, self.core.pl_rope_table(self._p(inv_freq), self._p(table), max_positions, half, self._stream))
+        _check(self.core, self.core.pl_rope_table(self._p(inv_freq), self._p(table), max_positions, half,
+                                                  c_float(magnitude), self._stream))
         self.launches += 1
         return table
 
-    def rope_kv_write(self, qkv, nh, nkv, d, position, ctx, kv, block_table, write=True):
+    def rope_kv_write(self, qkv, nh, nkv, d, position, ctx, kv, block_table, write=True, value_from_key=False):
         T = ctx.num_tokens
         assert qkv.is_contiguous() and qkv.shape[0] == T
         if position is not None:
@@ -394,7 +486,7 @@ class CudaOps:
         _check(self.core, self.core.pl_rope_kv_write(
             self._p(qkv), self._code(qkv), T, qkv.shape[1], self._p(table), table_len, rd, inter,
             self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
-            self._p(kv), num_pages, nh, nkv, d, ps, 1 if write else 0, self._stream))
+            self._p(kv), num_pages, nh, nkv, d, ps, 1 if write else 0, 1 if value_from_key else 0, self._stream))
         self.launches += 1
 
     # ---- attention ---------------------------------------------------------------
@@ -415,10 +507,10 @@ class CudaOps:
         return planning.is_long_context(num_requests, num_kv_heads, self.num_sms, self.MAX_SPLITS,
                                         self.MAX_CLUSTER if self.cluster_attention else 0, self.CLUSTER_KEYS, max_context)
 
-    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, chunk=None, pad_requests=None,
                        fixed_capacity=False, pad_tokens=None) -> dict:
         return planning.plan_attention(
-            q_lens, k_lens, group_size, num_kv_heads, window, small_rows=self.SMALL_ROWS,
+            q_lens, k_lens, group_size, num_kv_heads, window, chunk=chunk, small_rows=self.SMALL_ROWS,
             large_rows=self._large_rows(head_dim), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
             max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity,
             cluster_max=self.MAX_CLUSTER if self.cluster_attention else 0, long_keys=self.CLUSTER_KEYS,
@@ -443,35 +535,38 @@ class CudaOps:
                     and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS and not plan.long_context)
 
     def qkv_attention(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, scale, window, write=True,
-                      softcap=None, slopes=None) -> torch.Tensor:
+                      softcap=None, slopes=None, chunk=None, value_from_key=False) -> torch.Tensor:
         """The mixer's whole front: fused q/k/v projection, rotary positions on q and k, k and v written
         to the cache, attention over the pages.  Returns [T, nh * d].  It is `qkv_rope_write` followed by
         `paged_attention`, but for a decode step of more than 16 tokens (the projection is a library
         product then, without an epilogue) rotation and cache write happen inside the attention
         kernel instead of in a kernel of their own."""
         M = h.shape[0]
-        plan = ctx.attention_plans.get((nh // nkv, nkv, window, d))
+        plan = ctx.attention_plans.get(attention_plan_key(nh, nkv, window, d, chunk))
         inside = (plan is not None and write and softcap is None and slopes is None and position is not None
+                  and not value_from_key
                   and position.pairing == "half" and position.rotary_dim == d and M == ctx.num_tokens
                   and not self._skinny_ok(h, (nh + 2 * nkv) * d) and self.compute_dtype == torch.bfloat16
                   and kv.dtype == torch.bfloat16 and self._runs_as_clusters(plan, ctx, nh, nkv, True)
                   and self.rope_in_attention)
         if inside:
             qkv = self.linear(h, w_qkv)
-            return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, rope=position)
-        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
-        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes)
+            return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, rope=position, chunk=chunk)
+        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write,
+                                  value_from_key=value_from_key)
+        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes,
+                                    chunk=chunk)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
-                        rope=None):
+                        rope=None, chunk=None):
         """Attention of the step's tokens over the paged cache.  `softcap` (scores become
         softcap * tanh(score / softcap)) and `slopes` (a float32 tensor [nh]: head h adds
         slopes[h] * (key position - query position) to its scores) modify the scores; both off
-        by default.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
+        by default; `chunk` c lets a query at position p see the keys from p - p % c on only.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
         `qkv_attention`): qkv is the unrotated projection, and the kernel rotates q and the step's own
         keys and writes those keys and values to the cache itself."""
         T = ctx.num_tokens
-        plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
+        plan = ctx.attention_plans[attention_plan_key(nh, nkv, window, d, chunk)]
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
         p = AttnParams()
         real = sum(ctx.host.q_lens)
@@ -489,6 +584,7 @@ class CudaOps:
         p.nh, p.nkv, p.d, p.ps, p.num_pages = nh, nkv, d, kv.shape[3], kv.shape[0]
         p.window, p.scale, p.max_splits = int(window or 0), float(scale), plan.max_splits
         p.softcap = float(softcap or 0.0)
+        p.chunk = int(chunk or 0)
         if slopes is not None:
             assert slopes.dtype == torch.float32 and slopes.numel() == nh and slopes.is_contiguous() and slopes.is_cuda
             p.slopes = slopes.data_ptr()

@@ -89,16 +89,24 @@ def large_capacity(num_tokens: int, group_size: int, small_rows: int, large_rows
     return rows // large_rows + rows // (small_rows + 1) + 1
 
 
+def first_visible_key(pos: int, window: int | None, chunk: int | None) -> int:
+    """The lowest key position the query at `pos` sees: the last `window` keys, and none before its chunk."""
+    lo = max(0, pos - window + 1) if window else 0
+    if chunk:
+        lo = max(lo, pos - pos % chunk)
+    return lo
+
+
 def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: int | None, *, small_rows: int,
                    large_rows: int, min_split_keys: int, num_sms: int, max_splits: int = 32,
                    pad_requests: int | None = None, fixed_capacity: bool = False, cluster_max: int = 0,
-                   long_keys: int = 0, pad_tokens: int | None = None) -> dict:
+                   long_keys: int = 0, pad_tokens: int | None = None, chunk: int | None = None) -> dict:
     """`pad_tokens` (with `fixed_capacity`, for a step of mixed items that replays a captured graph): both lists
     get the capacity of any step of that many tokens and `pad_requests` requests, filled up with items of
     request -1 that the kernels skip."""
     S = len(q_lens)
     S_pad = pad_requests or S
-    if pad_tokens is None and S and max(q_lens) == 1 and group_size <= small_rows and not window:
+    if pad_tokens is None and S and max(q_lens) == 1 and group_size <= small_rows and not window and not chunk:
         return _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_splits, fixed_capacity,
                             cluster_max, long_keys)
     small_ids = [s for s in range(S) if q_lens[s] * group_size <= small_rows]
@@ -111,7 +119,7 @@ def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: i
     for s in small_ids:
         nq, lk = q_lens[s], k_lens[s]
         first_pos = lk - nq
-        lo = max(0, first_pos - window + 1) if window else 0
+        lo = first_visible_key(first_pos, window, chunk)
         n_keys = lk - lo
         ns = max(1, min(want, -(-n_keys // min_split_keys)))
         splits[s] = (ns, scratch_base)

@@ -1,4 +1,5 @@
 from .causal_lm import CacheSlot, CausalLM, build_model
 from .llama import llama_spec
+from .pomisun import pomisun_spec
 
-__all__ = ["CacheSlot", "CausalLM", "build_model", "llama_spec"]
+__all__ = ["CacheSlot", "CausalLM", "build_model", "llama_spec", "pomisun_spec"]

@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState,
-                          LazyLinear, ModelSpec, PagedKV, PartSpec, TensorSpec, make_part)
+                          LazyLinear, ModelSpec, PagedKV, PartSpec, TensorSpec, make_part, materialize)
 
 
 @dataclass(frozen=True)
@@ -45,7 +45,7 @@ class CausalLM:
         for layer in spec.layers:
             mixer_spec, extra = _resolve_positions(layer.mixer, self.positions)
             mixer = make_part(MIXERS, "mixer", mixer_spec, **extra)
-            ffn = make_part(FEED_FORWARDS, "feed-forward", layer.feed_forward)
+            ffn = make_part(FEED_FORWARDS, "feed-forward", layer.feed_forward) if layer.feed_forward is not None else None
             norms = {k: make_part(NORMS, "norm", ns) for k, ns in layer.norms.items()}
             try:
                 block_cls = BLOCKS[layer.block]
@@ -115,7 +115,12 @@ class CausalLM:
         `ctx.logits_indices` (None if nothing is wanted)."""
         x = self.embedding.forward(ctx.input_ids, ctx)
         pending = None
+        # the stream is summed up in place, so a model that adds the embedding's output again keeps a copy
+        again = x.clone() if any(e.add_embedding for e in self.schedule) else None
         for i, entry in enumerate(self.schedule):
+            if entry.add_embedding:
+                x = ctx.ops.add_rows(x, materialize(pending, ctx.ops), again)
+                pending = None
             x, pending = self.blocks[entry.layer].forward(x, pending, ctx, ctx.layer_caches[i])
         if ctx.num_logits == 0:
             return None

@@ -13,7 +13,11 @@ the keys at positions p-w+1 .. p.  Two score modifiers, off unless a spec asks
 for them (the reference has neither): `score_cap` c turns a scaled score s into
 c * tanh(s / c), and `position_slopes` (one number per query head) adds
 slope * (key position - query position) to it, a bias by distance that needs no
-rotation of q and k.
+rotation of q and k.  `chunk` c cuts the positions of a request into chunks of c,
+counted from position 0, and lets a query see only the keys of its own chunk;
+the cache gives the pages of finished chunks back.  `value_from_key`: there is
+no value projection; the value of a token is its key as projected, before the
+rotation (the cache still keeps both, since the stored key is rotated).
 """
 
 from __future__ import annotations
@@ -29,12 +33,17 @@ class PagedAttention(Mixer):
 
     def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float | None = None, window: int | None = None, position=None,
-                 score_cap: float | None = None, position_slopes=None):
+                 score_cap: float | None = None, position_slopes=None, chunk: int | None = None,
+                 value_from_key: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.window = window
+        if chunk is not None and not chunk > 0:
+            raise ValueError(f"chunk={chunk} must be positive")
+        self.chunk = int(chunk) if chunk else None
+        self.value_from_key = bool(value_from_key)
         self.position = position
         if score_cap is not None and not score_cap > 0:
             raise ValueError(f"score_cap={score_cap} must be positive")
@@ -48,23 +57,27 @@ class PagedAttention(Mixer):
         self.w_o = None
 
     def cache_requirement(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window, self.chunk)
 
     def attention_plan_key(self):
-        """(query heads per kv head, kv heads, window, head size): what the step's work lists depend on."""
-        return (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window, self.head_dim)
+        """(query heads per kv head, kv heads, window, head size[, chunk]): what the step's work lists depend on."""
+        key = (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window, self.head_dim)
+        return key + (self.chunk,) if self.chunk else key
 
     def tensor_specs(self):
         h, d = self.hidden_size, self.head_dim
-        return {
+        out = {
             self.names["q_proj"]: TensorSpec((self.num_heads * d, h)),
             self.names["k_proj"]: TensorSpec((self.num_kv_heads * d, h)),
-            self.names["v_proj"]: TensorSpec((self.num_kv_heads * d, h)),
             self.names["o_proj"]: TensorSpec((h, self.num_heads * d)),
         }
+        if not self.value_from_key:
+            out[self.names["v_proj"]] = TensorSpec((self.num_kv_heads * d, h))
+        return out
 
     def load(self, tensors):
-        self.w_qkv = torch.cat([tensors[self.names[k]] for k in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
+        stacked = ("q_proj", "k_proj") if self.value_from_key else ("q_proj", "k_proj", "v_proj")
+        self.w_qkv = torch.cat([tensors[self.names[k]] for k in stacked], dim=0).contiguous()
         self.w_o = tensors[self.names["o_proj"]].contiguous()
 
     def bytes_read_per_step(self):
@@ -75,7 +88,12 @@ class PagedAttention(Mixer):
         block_table = ctx.block_tables[cache.group]
         if self.position_slopes is not None and self._slopes is None:
             self._slopes = torch.tensor(self.position_slopes, dtype=torch.float32, device=cache.kv.device)
+        extra = {}
+        if self.chunk:
+            extra["chunk"] = self.chunk
+        if self.value_from_key:
+            extra["value_from_key"] = True
         o = ops.qkv_attention(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position, ctx,
                               cache.kv, block_table, self.scale, self.window, write=cache.owner,
-                              softcap=self.score_cap, slopes=self._slopes)
+                              softcap=self.score_cap, slopes=self._slopes, **extra)
         return LazyLinear(o, self.w_o)

@@ -41,7 +41,7 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None          # None: the layer has no feed-forward
     norms: dict[str, PartSpec]
 
 
@@ -50,10 +50,13 @@ class ScheduleEntry:
     """One run of a layer.  `layer` indexes `ModelSpec.layers`, so a layer may be
     named twice (its weights are shared, each run has a cache of its own).
     `cache_from` names an earlier schedule entry whose cache this run reads
-    instead of keeping one itself."""
+    instead of keeping one itself.  `add_embedding`: before this run the output
+    of the embedding (the stream as it was in front of the first run) is added
+    to the stream once more."""
 
     layer: int
     cache_from: int | None = None
+    add_embedding: bool = False
 
 
 @dataclass
@@ -76,7 +79,8 @@ class TensorSpec:
     role: "matrix" (a GEMM operand: kept in the compute dtype), "vector" (norm
     weights and the like: a tensor stored in 32-bit stays 32-bit, else compute
     dtype), "table_int" (integer tables: int32).
-    init: how the random-weights mode draws it: "normal", "norm" (1 or 1+noise).
+    init: how the random-weights mode draws it: "normal", "norm" (1 or 1+noise), "norm_zero" (0 or noise:
+    a norm weight stored as its deviation from 1).
     optional: may be absent from the checkpoint (e.g. a tied head).
     """
 
@@ -92,11 +96,14 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """The mixer keeps a key and a value vector per token, in pages.
-    `window`: only the last `window` tokens are ever read (None: all)."""
+    `window`: only the last `window` tokens are ever read (None: all).
+    `chunk`: positions are cut into chunks of this many, counted from 0, and a query reads
+    only the keys of its own chunk (None: no such cut)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)
@@ -223,28 +230,31 @@ class Block(Part):
     output not yet added, so that the sum can be fused with the next norm.
     """
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict[str, Norm]):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norms: dict[str, Norm]):
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+
+    def _parts(self):
+        return [p for p in (self.mixer, self.feed_forward, *self.norms.values()) if p is not None]
 
     def forward(self, x, pending, ctx, cache):
         raise NotImplementedError
 
     def tensor_specs(self):
         out = {}
-        for part in (self.mixer, self.feed_forward, *self.norms.values()):
+        for part in self._parts():
             out.update(part.tensor_specs())
         return out
 
     def load(self, tensors):
-        for part in (self.mixer, self.feed_forward, *self.norms.values()):
+        for part in self._parts():
             part.load(tensors)
 
     def bytes_read_per_step(self):
-        return sum(p.bytes_read_per_step() for p in (self.mixer, self.feed_forward, *self.norms.values()))
+        return sum(p.bytes_read_per_step() for p in self._parts())
 
     @property
     def capturable(self):
-        return all(p.capturable for p in (self.mixer, self.feed_forward, *self.norms.values()))
+        return all(p.capturable for p in self._parts())
 
 
 # --------------------------------------------------------------------------- registries

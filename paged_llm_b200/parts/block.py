@@ -1,6 +1,8 @@
 """Pre-norm arrangement: x += mixer(norm_in(x)); x += ffn(norm_post(x))
 (reference: pagedllm/model/llama.py:174-185).  Each residual sum is handed to
-the following norm as a pending branch so that one kernel does both."""
+the following norm as a pending branch so that one kernel does both.  A layer
+without a feed-forward (`feed_forward` None, no "post_mixer" norm) is
+x += mixer(norm_in(x)) alone."""
 
 from __future__ import annotations
 
@@ -16,6 +18,8 @@ class PreNormBlock(Block):
         if not self.mixer.accepts_lazy_input:
             h = ctx.ops.materialize(h)
         a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return x, a
         h = self.norms["post_mixer"].add_forward(x, a, ctx)
         if not self.feed_forward.accepts_lazy_input:
             h = ctx.ops.materialize(h)

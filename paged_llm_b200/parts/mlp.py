@@ -1,6 +1,7 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), no bias, act = SiLU
-(reference: pagedllm/model/llama.py:163-171).  Gate and up are stacked into one
-matrix [2*intermediate, hidden] when the weights are taken."""
+(reference: pagedllm/model/llama.py:163-171) or the tanh form of GELU,
+0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  Gate and up are stacked into
+one matrix [2*intermediate, hidden] when the weights are taken."""
 
 from __future__ import annotations
 
@@ -9,13 +10,16 @@ import torch
 from .base import FeedForward, LazyLinear, TensorSpec, register_feed_forward
 
 
+ACTIVATIONS = ("silu", "gelu_tanh")
+
+
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
     accepts_lazy_input = True
 
     def __init__(self, weights: dict[str, str], hidden_size: int, intermediate_size: int, activation: str = "silu"):
-        if activation != "silu":
-            raise ValueError(f"activation {activation!r} is not implemented (silu only)")
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not implemented ({', '.join(ACTIVATIONS)} only)")
         self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
         self.names = weights
         self.w_gate_up = None
@@ -38,4 +42,6 @@ class GatedMLP(FeedForward):
 
     def forward(self, h, ctx):
         ops = ctx.ops
-        return LazyLinear(ops.gated_silu_linear(h, self.w_gate_up), self.w_down)
+        if self.activation == "silu":
+            return LazyLinear(ops.gated_silu_linear(h, self.w_gate_up), self.w_down)
+        return LazyLinear(ops.gated_act_linear(h, self.w_gate_up, self.activation), self.w_down)

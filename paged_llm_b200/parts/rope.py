@@ -34,6 +34,26 @@ def llama3_rescale(inv_freq: torch.Tensor, factor: float, low_freq_factor: float
     return torch.where(band, (1 - blend) * inv_freq / factor + blend * inv_freq, out)
 
 
+def yarn_rescale(inv_freq: torch.Tensor, base: float, factor: float, original: float, fast: float,
+                 slow: float) -> tuple[torch.Tensor, float]:
+    """YaRN: pair i of r/2 keeps its frequency if it turns fast and gets 1/factor of it if it turns
+    slowly, with a linear ramp between.  With pair(t) = r ln(original / (2 pi t)) / (2 ln base) the
+    pair whose wave makes t turns over `original` positions, lo = max(floor(pair(fast)), 0),
+    hi = min(ceil(pair(slow)), r - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    the frequency is f_i / factor * ramp_i + f_i * (1 - ramp_i).  Cosine and sine are both
+    multiplied by 0.1 ln(factor) + 1, which is returned beside the frequencies."""
+    f = inv_freq.double()
+    r = 2 * f.numel()
+
+    def pair(turns: float) -> float:
+        return r * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair(fast)), 0)
+    hi = min(math.ceil(pair(slow)), r - 1)
+    ramp = ((torch.arange(f.numel(), dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).float(), 0.1 * math.log(factor) + 1.0
+
+
 @register_position_encoding("rotary")
 class RotaryEncoding(PositionEncoding):
     def __init__(self, weights: dict[str, str], head_dim: int, theta: float,
@@ -49,16 +69,29 @@ class RotaryEncoding(PositionEncoding):
         self.max_positions = 0
 
     def inv_freq(self) -> torch.Tensor:
+        return self.frequencies()[0]
+
+    def frequencies(self) -> tuple[torch.Tensor, float]:
+        """(frequency of each pair in float32, the factor cosine and sine are multiplied by)."""
         rd = self.rotary_dim
+        kind = (self.scaling or {}).get("rope_type", (self.scaling or {}).get("type"))
+        if kind == "yarn":
+            # formed in float64 and rounded once
+            inv = self.theta ** (-torch.arange(0, rd, 2, dtype=torch.float64) / rd)
+            sc = self.scaling
+            return yarn_rescale(inv, self.theta, float(sc["factor"]), float(sc["original"]), float(sc["fast"]),
+                                float(sc["slow"]))
         inv = 1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))
-        if self.scaling:
-            kind = self.scaling.get("rope_type", self.scaling.get("type"))
-            if kind == "llama3":
-                inv = llama3_rescale(inv, **{k: v for k, v in self.scaling.items() if k not in ("rope_type", "type")})
-            elif kind not in (None, "default"):
-                raise NotImplementedError(f"rope_type={kind!r} not supported (default and llama3 only)")
-        return inv
+        if kind == "llama3":
+            inv = llama3_rescale(inv, **{k: v for k, v in self.scaling.items() if k not in ("rope_type", "type")})
+        elif kind not in (None, "default"):
+            raise NotImplementedError(f"rope_type={kind!r} not supported (default, llama3 and yarn only)")
+        return inv, 1.0
 
     def prepare(self, max_positions, device, ops):
         self.max_positions = int(max_positions)
-        self.table = ops.rope_table(self.inv_freq().to(device), self.max_positions)
+        inv, magnitude = self.frequencies()
+        if magnitude == 1.0:
+            self.table = ops.rope_table(inv.to(device), self.max_positions)
+        else:
+            self.table = ops.rope_table(inv.to(device), self.max_positions, magnitude)

@@ -49,10 +49,42 @@ class TorchOps:
         return y if out_float32 else y.to(self.compute_dtype)
 
     def silu_mul(self, gate_up):
+        return self.act_mul(gate_up, "silu")
+
+    def act_mul(self, gate_up, activation="silu"):
         self._count("silu_mul")
         i = gate_up.shape[1] // 2
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
-        return (g * torch.sigmoid(g) * u).to(self.compute_dtype)
+        a = g * torch.sigmoid(g) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+        return (a * u).to(self.compute_dtype)
+
+    def add_rows(self, x, branch=None, extra=None):
+        if branch is not None:
+            x += branch.float()
+        if extra is not None:
+            x += extra
+        return x
+
+    def gated_act_linear(self, h, w_gate_up, activation="silu"):
+        return self.act_mul(self.linear(h, w_gate_up), activation)
+
+    def routed_experts(self, h, w_router, w_gate_up, w_down, top_k, activation="silu", shared=None,
+                       shared_activation="silu"):
+        self._count("routed_experts")
+        E = w_gate_up.shape[0]
+        z = h.float() @ w_router.float().T
+        top, idx = torch.topk(z[:, :E], top_k, dim=-1)
+        wt = torch.softmax(top, dim=-1)
+        y = torch.zeros(h.shape[0], w_down.shape[1], dtype=torch.float32, device=h.device)
+        for t in range(h.shape[0]):
+            for j in range(top_k):
+                e = int(idx[t, j])
+                inter = self.act_mul(self.linear(h[t:t + 1], w_gate_up[e]), activation)
+                y[t] += wt[t, j] * self.linear(inter, w_down[e]).float()[0]
+        if shared is not None:
+            s = self.linear(self.gated_act_linear(h, shared[0], shared_activation), shared[1]).float()
+            y += torch.sigmoid(z[:, E:E + 1]) * s
+        return y
 
     def materialize(self, h):
         return h
@@ -63,30 +95,32 @@ class TorchOps:
     def gated_silu_linear(self, h, w_gate_up):
         return self.silu_mul(self.linear(h, w_gate_up))
 
-    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True):
+    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True, value_from_key=False):
         qkv = self.linear(h, w_qkv)
-        self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+        self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write, value_from_key=value_from_key)
         return qkv
 
     def qkv_attention(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, scale, window, write=True,
-                      softcap=None, slopes=None):
-        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
-        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes)
+                      softcap=None, slopes=None, chunk=None, value_from_key=False):
+        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write,
+                                  value_from_key=value_from_key)
+        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes,
+                                    chunk=chunk)
 
     def gather_rows(self, x, idx):
         return x[idx.long()].clone()
 
     # ---- positions -------------------------------------------------------------
-    def rope_table(self, inv_freq, max_positions):
+    def rope_table(self, inv_freq, max_positions, magnitude=1.0):
         ang = torch.outer(torch.arange(max_positions, dtype=torch.float32), inv_freq.float().cpu())
-        return torch.stack([ang.cos(), ang.sin()], dim=-1).to(self.device)
+        return (torch.stack([ang.cos(), ang.sin()], dim=-1) * magnitude).to(self.device)
 
-    def rope_kv_write(self, qkv, nh, nkv, d, position, ctx, kv, block_table, write=True):
+    def rope_kv_write(self, qkv, nh, nkv, d, position, ctx, kv, block_table, write=True, value_from_key=False):
         self._count("rope_kv_write")
         T = ctx.num_tokens
         q = qkv[:, :nh * d].view(T, nh, d)
         k = qkv[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
-        v = qkv[:, (nh + nkv) * d:].view(T, nkv, d)
+        v = k.clone() if value_from_key else qkv[:, (nh + nkv) * d:].view(T, nkv, d)
         pos = ctx.positions.long()
         if position is not None:
             rd = position.rotary_dim
@@ -114,13 +148,14 @@ class TorchOps:
                 kv[page, 1, :, p % ps, :] = v[t].to(kv.dtype)
 
     # ---- attention -------------------------------------------------------------
-    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, chunk=None, pad_requests=None,
                        fixed_capacity=False, pad_tokens=None):
-        return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
+        return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, chunk=chunk, small_rows=16, large_rows=64,
                               min_split_keys=128, num_sms=4, pad_requests=pad_requests, fixed_capacity=fixed_capacity,
                               pad_tokens=pad_tokens)
 
-    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None):
+    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
+                        chunk=None):
         self._count("paged_attention")
         T = ctx.num_tokens
         q = qkv[:, :nh * d].view(T, nh, d).float()
@@ -131,6 +166,8 @@ class TorchOps:
         for s, (nq, lk) in enumerate(zip(ctx.host.q_lens, ctx.host.k_lens)):
             first = lk - nq
             lo = max(0, first - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, first - first % chunk)
             idx = torch.arange(lo, lk)
             pages = block_table[s, (idx // ps)].long()
             assert (pages >= 0).all(), "read of a page that was given back"
@@ -148,6 +185,8 @@ class TorchOps:
             hidden = idx[None, :] > qpos[:, None]
             if window:
                 hidden |= idx[None, :] <= qpos[:, None] - window
+            if chunk:
+                hidden |= idx[None, :] < (qpos - qpos % chunk)[:, None]
             scores = scores.masked_fill(hidden[None], float("-inf"))
             o = torch.einsum("hqk,khd->qhd", scores.softmax(-1), v)
             out[cu[s]:cu[s + 1]] = o.reshape(nq, nh * d).to(self.compute_dtype)
