@@ -75,6 +75,20 @@ def chunk_visible(n: int, chunk: int | None):
     return vis
 
 
+def attend(q, k, v, scale: float, softcap: float | None = None, chunk: int | None = None):
+    """q: [n, H, d], k and v: [n, G, d] of one whole sequence -> [n, H, d].  Query head h reads
+    key/value head h // (H / G); scores are capped, then masked, then softmaxed."""
+    n, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
+    kk = k.repeat_interleave(rep, dim=1)
+    vv = v.repeat_interleave(rep, dim=1)
+    s = torch.einsum("ihd,jhd->hij", q, kk) * float(scale)
+    if softcap:
+        s = float(softcap) * torch.tanh(s / float(softcap))
+    s = s.masked_fill(~chunk_visible(n, chunk)[None], float("-inf"))
+    return torch.einsum("hij,jhd->ihd", torch.softmax(s, dim=-1), vv)
+
+
 def attention(h, m: dict, w: dict):
     """h: [n, D]; m: the mixer's sizes and constants; w: 'q', 'k', 'o' matrices [out, in]."""
     n = h.shape[0]
@@ -85,18 +99,13 @@ def attention(h, m: dict, w: dict):
     pos = torch.arange(n)
     if m.get("rot"):
         q, k = rotate(q, pos, m["rot"]), rotate(k, pos, m["rot"])
-    rep = H // G
-    kk = k.repeat_interleave(rep, dim=1)
-    vv = v.repeat_interleave(rep, dim=1)
-    s = torch.einsum("ihd,jhd->hij", q, kk) * float(m["scale"])
-    cap = m.get("softcap")
-    if cap:
-        s = float(cap) * torch.tanh(s / float(cap))
-    chunk = (m.get("mask") or {}).get("size")
-    s = s.masked_fill(~chunk_visible(n, chunk)[None], float("-inf"))
-    p = torch.softmax(s, dim=-1)
-    o = torch.einsum("hij,jhd->ihd", p, vv).reshape(n, H * d)
-    return o @ w["o"].T
+    o = attend(q, k, v, m["scale"], m.get("softcap"), (m.get("mask") or {}).get("size"))
+    return o.reshape(n, H * d) @ w["o"].T
+
+
+# a test may set this to a list: every routed layer run then appends the smallest distance, in units of the
+# logits' spread, between the last chosen and the first rejected expert over the sequence's tokens
+ROUTER_MARGINS: list | None = None
 
 
 def gated(h, w: dict, act):
@@ -108,6 +117,9 @@ def routed(h, mlp: dict, w: dict, prefix: str):
     shared expert, if there is one, is added times the sigmoid of one number per token."""
     E, k = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     z = h @ w[prefix + "router"].T                                   # [n, E]
+    if ROUTER_MARGINS is not None and k < E:
+        ranked = z.sort(dim=-1, descending=True).values
+        ROUTER_MARGINS.append(float(((ranked[:, k - 1] - ranked[:, k]) / z.std()).min()))
     top, idx = torch.topk(z, k, dim=-1)
     wt = torch.softmax(top, dim=-1)
     out = torch.zeros_like(h)
