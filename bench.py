@@ -61,6 +61,18 @@ SIZES = {
     "tiny-a": dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=4096),
 }
+# Layer sizes for `--only pomisun`: the Pomisun decoder (dense and routed-expert layers in turn, the first two run
+# twice, chunked mask, score cap, YaRN) beside a Llama of the same width, heads, dense inner size and number of
+# layer runs.
+POMISUN_SIZES = {
+    "p-2k": dict(vocab=32000, width=2048, heads=16, kv_heads=4, dim=128, ff=8192, experts=32, top=4, expert_ff=1024,
+                 shared_ff=2048, chunk=1024, layers=4, loop=dict(start=0, stop=2, times=2)),
+    "p-4k": dict(vocab=32000, width=4096, heads=32, kv_heads=8, dim=128, ff=14336, experts=64, top=6, expert_ff=1408,
+                 shared_ff=2816, chunk=2048, layers=4, loop=None),
+    # for trying the option out quickly; never a result
+    "p-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, experts=4, top=2, expert_ff=64,
+                   shared_ff=64, chunk=64, layers=2, loop=None),
+}
 PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
 RAGGED_PROMPTS, RAGGED_OUTPUTS = (128, 4096), (64, 512)      # the ragged serving workload: lengths drawn uniformly
 
@@ -549,11 +561,81 @@ def validate(args) -> dict:
             "trace": "2,048-token portion + 32 decoded tokens; three requests of 700/333/90 tokens mixed, portions of 2 to 257 tokens"}
 
 
+def pomisun_configs(name: str):
+    """(Pomisun configuration dict, Llama configuration dict of equal size, number of layer runs)."""
+    s = POMISUN_SIZES[name]
+    mixer = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+             "softcap": 50.0, "mask": {"size": s["chunk"]},
+             "rot": {"dims": s["dim"], "base": 1000000.0,
+                     "scaling": {"factor": 2.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["shared_ff"]}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(s["layers"])]
+    pom = {"architecture": "Pomisun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "layers": layers}
+    runs = s["layers"]
+    if s["loop"]:
+        pom["loop"] = dict(s["loop"])
+        runs += (s["loop"]["stop"] - s["loop"]["start"]) * (s["loop"]["times"] - 1)
+    llama = {"architectures": ["LlamaForCausalLM"], "vocab_size": s["vocab"], "hidden_size": s["width"],
+             "intermediate_size": s["ff"], "num_hidden_layers": runs, "num_attention_heads": s["heads"],
+             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+             "tie_word_embeddings": True, "max_position_embeddings": 8192}
+    return pom, llama, runs
+
+
+def pomisun_compare(args) -> dict:
+    """Prefill and decode of the Pomisun decoder at layer sizes of a real model (random weights drawn on the
+    device) beside a Llama of equal width, heads and layer runs: device-timed with CUDA events, with the device
+    time of every kernel inside the steps for the roofline of each."""
+    import torch
+    from paged_llm_b200 import EngineConfig, LLMEngine
+    from paged_llm_b200.config.registry import parse_model_config
+    from paged_llm_b200.weights import write_random_stub
+
+    pom, llama, runs = pomisun_configs(args.pomisun_size)
+    pre = args.prefill_tokens or PREFILL_TOKENS
+    ctx_len = args.context or PROMPT_LEN
+    steps = min(args.steps, 64)
+    batches = (8, 64) if args.batch == 8 else (args.batch,)
+    max_len = max(ctx_len + steps + args.warmup + 16, pre) + 64
+    out = {"only": "pomisun", "size": args.pomisun_size, "layer_runs": runs, "prefill_tokens": pre, "context": ctx_len,
+           "sizes": POMISUN_SIZES[args.pomisun_size], "peaks": load_peaks()}
+    for arm, hf in (("pomisun", pom), ("llama", llama)):
+        with tempfile.TemporaryDirectory() as folder:
+            _, cfg = parse_model_config(hf)
+            write_random_stub(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
+            seqs = max(batches)
+            engine = LLMEngine(folder, EngineConfig(
+                dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
+                max_num_batched_tokens=max(2048, pre), enable_prefix_caching=False,
+                num_gpu_blocks=seqs * (-(-max_len // BLOCK_SIZE)) + 64))
+        res = {"params": cfg.num_parameters, "weight_bytes_per_decode_step": engine.model.weight_bytes_per_step()}
+        ms = prefill_once(engine, pre)
+        res["prefill_ms"] = round(ms, 3)
+        res["prefill_tokens_per_s"] = round(pre * 1000.0 / ms, 1)
+        if args.kernel_times:
+            res["prefill_kernels"] = prefill_kernel_times(engine, pre)
+        for B in batches:
+            ms, launches, ctx_mid = device_decode_loop(engine, B, steps, args.warmup, ctx_len)
+            res[f"decode_b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B * 1000.0 / ms, 1),
+                                   "launches_per_step": launches, "context": ctx_mid}
+            if args.kernel_times:
+                res[f"decode_b{B}"]["kernels"] = decode_kernel_times(engine, B, min(steps, 8), args.warmup, ctx_len)
+        engine.ops.check_kernels()
+        out[arm] = res
+        del engine
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
     from paged_llm_b200 import EngineConfig, LLMEngine
 
     peaks = load_peaks()
+    if args.only == "pomisun":
+        return pomisun_compare(args)
     if args.only == "validate":
         return validate(args)
     if args.only == "sample":
@@ -746,10 +828,13 @@ def main() -> int:
     ap.add_argument("--output-range", default=None, help="with --only ragged: LO,HI output lengths (default 64,512)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only decode or --only prefill: add the device time of every kernel inside the replayed steps")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample"], default=None,
+    ap.add_argument("--pomisun-size", choices=sorted(POMISUN_SIZES), default="p-2k",
+                    help="with --only pomisun: the layer sizes (the Llama beside it gets the same)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
-                         "portion of --prefill-tokens), the float32 validation run, or the sampler's kernels on --batch rows, and print "
+                         "portion of --prefill-tokens), the float32 validation run, the sampler's kernels on --batch rows, or "
+                         "prefill and decode of the Pomisun decoder beside a Llama of equal size (--pomisun-size), and print "
                          "a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
