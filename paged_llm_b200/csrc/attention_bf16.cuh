@@ -667,6 +667,14 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     // tile in all forms (three blocks per SM instead of one: 1.7 times the speed); head size 256 keeps
     // 64 keys and two stages, which is what fits.
     constexpr int KPW_CLUSTER = PL_DPAD <= 64 ? 32 : 16;
+#if PL_DPAD == 64 || PL_DPAD == 128
+    // prompt portions of head sizes 64 and 128 with a cap on the scores (and no bias by distance): the
+    // tcgen05 kernel applies the cap itself
+    static const bool no_tc_cap = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
+    if (p.softcap > 0.f && p.slopes == nullptr && p.rope_table == nullptr && p.cluster <= 0 && !p.is_small &&
+        p.d == PL_DPAD && !no_tc_cap && tc2::takes(p))
+        return tc2::launch<PL_DPAD>(p, stream);
+#endif
     if (p.softcap > 0.f || p.slopes != nullptr) {
         PL_REQUIRE(p.rope_table == nullptr, "attention_bf16: score modifiers and rotary positions inside the kernel "
                                             "do not combine");
@@ -707,9 +715,10 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
 #if PL_DPAD == 64
     static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
-    if (p.d == 64 && !no_tc && p.chunk <= 0) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);
+    if (p.d == 64 && !no_tc && (p.chunk <= 0 || (!serial_tc && tc2::takes(p))))
+        return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);
 #else
-    if (p.d == 128 && !no_tc && p.chunk <= 0 && tc2::takes(p)) return tc2::launch<128>(p, stream);
+    if (p.d == 128 && !no_tc && tc2::takes(p)) return tc2::launch<128>(p, stream);
 #endif
 #endif
     return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64>(p, stream);

@@ -566,6 +566,13 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16);
         const uint32_t tmem_o = tmem_row + 128;
         const float scale_log2 = p.scale * 1.4426950408889634f;
+        const int first = attn_first_key(p, max(pos, 0));      // the lowest key this row sees (window, chunk)
+        // A cap c on the scaled scores: s -> c tanh(s / c).  Kept in units of the raw product (the scale is
+        // applied below): x -> (c / scale) tanh(x scale / c), with tanh(y) = 1 - 2 / (1 + e^(2 y)) from one
+        // exponential and one reciprocal (both ends saturate correctly: e = inf gives 1, e = 0 gives -1).
+        const bool capped = p.softcap > 0.f;
+        const float cap_in = capped ? 2.f * 1.4426950408889634f * p.scale / p.softcap : 0.f;
+        const float cap_out = capped ? p.softcap / p.scale : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         float sv[64];
         for (int t = 0; t < n_tiles; ++t) {
@@ -575,13 +582,21 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             fence_after_sync();
             tmem_ld64(tmem_row + b * 64, sv);
             const int kbase = key0 + t * BN;
-            const bool row_full = p.window <= 0 && kbase >= it.key_lo && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
+            if (capped) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    float r;
+                    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(1.f + ex2(sv[i] * cap_in)));
+                    sv[i] = fmaf(-2.f * cap_out, r, cap_out);
+                }
+            }
+            const bool row_full = kbase >= it.key_lo && kbase >= first && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
             const bool warp_full = __all_sync(0xffffffffu, row_full);
             if (!warp_full) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int n = kbase + i;
-                    const bool vis = n >= it.key_lo && n < it.key_hi && n <= pos && (p.window <= 0 || n > pos - p.window);
+                    const bool vis = n >= it.key_lo && n < it.key_hi && n <= pos && n >= first;
                     sv[i] = vis ? sv[i] : -INFINITY;
                 }
             }

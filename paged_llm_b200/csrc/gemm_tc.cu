@@ -14,3 +14,17 @@ PL_EXPORT int pl_gemm_tc(const void* X, int ldx, const void* W, void* Y, int ldy
                          cudaStream_t stream) {
     return gemm_tc_duo_launch(X, ldx, W, Y, ldy, resid, M, N, K, epi, stream);
 }
+
+// The same with the gate's activation chosen: act 0 SiLU, 1 the tanh form of GELU (epilogue 2 only).
+PL_EXPORT int pl_gemm_tc_act(const void* X, int ldx, const void* W, void* Y, int ldy, int M, int N, int K, int act,
+                             cudaStream_t stream) {
+    return gemm_tc_duo_launch(X, ldx, W, Y, ldy, nullptr, M, N, K, TC_SILU, stream, act);
+}
+
+// Grouped: X [cap, K] holds rows sorted by expert in tiles of 256 (tile i belongs to expert tile_expert[i], *n_tiles
+// tiles are in use), W is [experts][N (or 2N for epilogue 2)][K]; Y [cap, ldy] in the order of X.  epi 0, 1 or 2.
+PL_EXPORT int pl_gemm_tc_grouped(const void* X, int ldx, const void* W, void* Y, int ldy, int cap, int N, int K, int epi,
+                                 int act, int experts, const int* n_tiles, const int* tile_expert, cudaStream_t stream) {
+    PL_REQUIRE(experts > 0, "gemm_tc_grouped: experts=%d", experts);
+    return gemm_tc_duo_launch(X, ldx, W, Y, ldy, nullptr, cap, N, K, epi, stream, act, experts, n_tiles, tile_expert);
+}

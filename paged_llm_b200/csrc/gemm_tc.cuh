@@ -6,7 +6,8 @@
 //
 // Epilogues (the rows of W behind a tile are chosen so that no second kernel is needed):
 //   plain  256 consecutive rows;                      y = acc (bfloat16 or float32)
-//   SiLU   128 gate rows and the 128 matching up rows; y = silu(gate) * up  (xiyiji/paged-llm llama.py:171)
+//   SiLU   128 gate rows and the 128 matching up rows; y = silu(gate) * up  (xiyiji/paged-llm llama.py:171),
+//          or with the tanh form of GELU in place of SiLU
 //   add    the product is a branch of the residual stream: x += bf16(acc) in float32 (llama.py:183-184)
 #pragma once
 
@@ -21,6 +22,12 @@ struct TcParams {
     int ldy, M, N, K, I;
     int epi;
     int m_tiles, n_tiles;
+    int act;                    // SiLU epilogue: the gate's activation (0 SiLU, 1 the tanh form of GELU)
+    // Grouped form (null / 0: one W for all rows): the rows of X are sorted by expert in tiles of 256, tile mp
+    // multiplies the rows of W that start at tile_expert[mp] * expert_rows, and only *m_pairs_dev tiles exist.
+    const int* m_pairs_dev;
+    const int* tile_expert;
+    int expert_rows;
 };
 
 namespace {
@@ -63,7 +70,7 @@ __device__ __forceinline__ void tc_drain_row(const TcParams& p, uint32_t acc, in
                         for (int e = 0; e < 2; ++e) {
                             const float gate = __bfloat162float(__float2bfloat16_rn(g[q * 8 + 2 * i + e]));
                             const float up = __bfloat162float(__float2bfloat16_rn(u[q * 8 + 2 * i + e]));
-                            o[e] = gate / (1.0f + __expf(-gate)) * up;
+                            o[e] = (p.act == 1 ? gelu_tanh_f(gate) : gate / (1.0f + __expf(-gate))) * up;
                         }
                         w[i] = pack_bf16x2(o[0], o[1]);
                     }

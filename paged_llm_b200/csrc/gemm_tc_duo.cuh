@@ -81,8 +81,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
     const bool leader = rank == 0;
-    const int m_pairs = p.m_tiles / 2;
-    const int tiles = m_pairs * p.n_tiles;
+    // (grouped form: the number of tiles in use is on the device; it is written by a kernel in front)
+    int m_pairs = p.m_tiles / 2;
     const int first = blockIdx.x / 2, stride = gridDim.x / 2;
     const int k_steps = p.K / TC_BK;
 
@@ -111,6 +111,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t tmem_base = tmem_base_slot;
+    if (p.m_pairs_dev != nullptr) m_pairs = max(0, min(m_pairs, *p.m_pairs_dev));
+    const int tiles = m_pairs * p.n_tiles;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- copies (both blocks)
@@ -122,7 +124,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
                 duo_tile(tile, m_pairs, p.n_tiles, nt, mp);
                 const int mt = mp * 2 + (int)rank;
                 // this block's half of the 256 rows of W: the first 128 (gate rows) or the second (up rows)
-                const int w_row = p.epi == TC_SILU ? (leader ? nt * 128 : p.I + nt * 128) : nt * 256 + (int)rank * 128;
+                const int w_base = p.tile_expert != nullptr ? p.tile_expert[mp] * p.expert_rows : 0;
+                const int w_row = w_base + (p.epi == TC_SILU ? (leader ? nt * 128 : p.I + nt * 128) : nt * 256 + (int)rank * 128);
                 for (int ks = 0; ks < k_steps; ++ks, ++it) {
                     const int s = it % DUO_STAGES;
                     if (it >= DUO_STAGES && !mbar_wait(&empty[s], ((it / DUO_STAGES) - 1) & 1)) {
@@ -193,9 +196,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
 }
 
-// The same checks and interface as gemm_tc_launch.
+// The same checks and interface as gemm_tc_launch.  Grouped form (experts > 0): W is [experts][rows][K] and the
+// rows of X are sorted by expert in tiles of 256 (see TcParams); M is the capacity of X.
 int gemm_tc_duo_launch(const void* X, int ldx, const void* W, void* Y, int ldy, float* resid, int M, int N, int K, int epi,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int act = 0, int experts = 0, const int* m_pairs_dev = nullptr,
+                       const int* tile_expert = nullptr) {
+    PL_REQUIRE(act == 0 || act == 1, "gemm_tc_duo: activation %d", act);
+    PL_REQUIRE(experts == 0 || (m_pairs_dev != nullptr && tile_expert != nullptr && M % 256 == 0 && epi != TC_ADD),
+               "gemm_tc_duo: the grouped form needs the tile list and a capacity that is a multiple of 256");
     PL_REQUIRE(epi >= TC_BF16 && epi <= TC_ADD, "gemm_tc_duo: epilogue %d", epi);
     PL_REQUIRE(M >= 1 && N >= 1 && K >= 64 && K % 64 == 0 && ldx % 8 == 0 && (epi == TC_ADD || ldy % 8 == 0),
                "gemm_tc_duo: M=%d N=%d K=%d (multiple of 64) ldx=%d ldy=%d", M, N, K, ldx, ldy);
@@ -218,9 +226,13 @@ int gemm_tc_duo_launch(const void* X, int ldx, const void* W, void* Y, int ldy, 
     p.K = K;
     p.I = N;
     p.epi = epi;
+    p.act = act;
+    p.m_pairs_dev = m_pairs_dev;
+    p.tile_expert = tile_expert;
     p.m_tiles = ((M + TC_BM - 1) / TC_BM + 1) / 2 * 2;
     p.n_tiles = epi == TC_SILU ? (N + 127) / 128 : (N + TC_BN - 1) / TC_BN;
-    const int w_rows = epi == TC_SILU ? 2 * N : N;
+    const int w_rows = (epi == TC_SILU ? 2 * N : N) * (experts > 0 ? experts : 1);
+    p.expert_rows = experts > 0 ? (epi == TC_SILU ? 2 * N : N) : 0;
     alignas(64) CUtensorMap x_map, w_map;
     if (!tensor_map_bf16(&x_map, X, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldx, 128) ||
         !tensor_map_bf16(&w_map, W, (unsigned long long)w_rows, (unsigned long long)K, (unsigned long long)K, 128))

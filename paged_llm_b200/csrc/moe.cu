@@ -17,75 +17,129 @@ namespace {
 __device__ __forceinline__ float act_f(int act, float z) { return act == 1 ? gelu_tanh_f(z) : silu_f(z); }
 
 // ------------------------------------------------------------------ router
-// One warp per token.  logits[e] = sum_c h[c] * W[e][c] in float32 for the E experts and, if `shared_gate`,
-// one more row of W whose sigmoid is the token's factor for the shared expert.
-template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ W,
-                                                        int tokens, int D, int E, int k, int shared_gate,
-                                                        int* __restrict__ top_idx, float* __restrict__ top_w,
-                                                        float* __restrict__ gate) {
-    extern __shared__ float z_all[];                    // [4][E + 1]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= tokens) return;
-    float* z = z_all + warp * (E + 1);
-    const T* x = h + (size_t)t * ldh;
-    const int rows = E + (shared_gate ? 1 : 0);
-    for (int e = 0; e < rows; ++e) {
-        const T* w = W + (size_t)e * D;
-        float s = 0.f;
-        for (int c = lane; c < D; c += 32) s = fmaf(to_float(x[c]), to_float(w[c]), s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s;
+// A block of 8 warps takes RT_TOK tokens.  logits[t][e] = sum_c h[t][c] * W[e][c] in float32 for the E experts
+// and, if `shared_gate`, one more row of W whose sigmoid is the token's factor for the shared expert: the
+// warps share the rows of W between them, a lane reads 16 bytes of a row once and multiplies them into all
+// the block's tokens (whose rows stay in L1).  Then warp t picks the k largest of token t, one after the
+// other (among equals the lowest index), and forms the softmax over the chosen.
+constexpr int RT_TOK = 8, RT_WARPS = 8;
+
+template <typename T> struct Ld16 {};
+template <> struct Ld16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     }
-    __syncwarp();
-    if (shared_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
-    // the k largest, one after the other; among equals the lowest index
-    float chosen_z = 0.f, z_max = 0.f, sum = 0.f;
-    int chosen_e = -1;                                  // lane j keeps choice j (k <= 32)
-    for (int j = 0; j < k; ++j) {
-        float best = -INFINITY;
-        int arg = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > best || (v == best && e < arg)) {
-                best = v;
-                arg = e;
+};
+template <> struct Ld16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __low2float(h2[i]);
+            v[2 * i + 1] = __high2float(h2[i]);
+        }
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ W,
+                                                                  int tokens, int D, int E, int k, int shared_gate, int vec,
+                                                                  int* __restrict__ top_idx, float* __restrict__ top_w,
+                                                                  float* __restrict__ gate) {
+    extern __shared__ float z_all[];                    // [RT_TOK][E + 1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * RT_TOK;
+    const int nt = min(RT_TOK, tokens - t0);
+    const int rows = E + (shared_gate ? 1 : 0);
+    constexpr int N = Ld16<T>::N;
+    for (int e = warp; e < rows; e += RT_WARPS) {
+        const T* w = W + (size_t)e * D;
+        float acc[RT_TOK];
+#pragma unroll
+        for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
+        if (vec) {
+            for (int c = lane * N; c < D; c += 32 * N) {
+                float wv[8], xv[8];
+                Ld16<T>::load(w + c, wv);
+#pragma unroll
+                for (int t = 0; t < RT_TOK; ++t) {
+                    if (t < nt) {
+                        Ld16<T>::load(h + (size_t)(t0 + t) * ldh + c, xv);
+#pragma unroll
+                        for (int i = 0; i < N; ++i) acc[t] = fmaf(xv[i], wv[i], acc[t]);
+                    }
+                }
+            }
+        } else {
+            for (int c = lane; c < D; c += 32) {
+                const float wv = to_float(w[c]);
+#pragma unroll
+                for (int t = 0; t < RT_TOK; ++t)
+                    if (t < nt) acc[t] = fmaf(to_float(h[(size_t)(t0 + t) * ldh + c]), wv, acc[t]);
             }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ob > best || (ob == best && oa < arg)) {
-                best = ob;
-                arg = oa;
-            }
+        for (int t = 0; t < RT_TOK; ++t) {
+            const float s = warp_sum(acc[t]);
+            if (lane == 0) z_all[t * (E + 1) + e] = s;
         }
-        if (arg >= E) arg = 0;                          // (only if every logit is NaN)
-        if (j == 0) z_max = best;
-        if (lane == j) {
-            chosen_z = best;
-            chosen_e = arg;
-        }
-        __syncwarp();
-        if (lane == 0) z[arg] = -INFINITY;
-        __syncwarp();
     }
-    const float pj = lane < k ? expf(chosen_z - z_max) : 0.f;
-    sum = warp_sum(pj);
-    if (lane < k) {
-        top_idx[(size_t)t * k + lane] = chosen_e;
-        top_w[(size_t)t * k + lane] = pj / sum;
+    __syncthreads();
+    for (int tl = warp; tl < nt; tl += RT_WARPS) {
+        const int t = t0 + tl;
+        float* z = z_all + tl * (E + 1);
+        if (shared_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
+        float chosen_z = 0.f, z_max = 0.f;
+        int chosen_e = -1;                                  // lane j keeps choice j (k <= 32)
+        for (int j = 0; j < k; ++j) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = z[e];
+                if (v > best || (v == best && e < arg)) {
+                    best = v;
+                    arg = e;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) {
+                    best = ob;
+                    arg = oa;
+                }
+            }
+            if (arg >= E) arg = 0;                          // (only if every logit left is NaN)
+            if (j == 0) z_max = best;
+            if (lane == j) {
+                chosen_z = best;
+                chosen_e = arg;
+            }
+            __syncwarp();
+            if (lane == 0) z[arg] = -INFINITY;
+            __syncwarp();
+        }
+        const float pj = lane < k ? expf(chosen_z - z_max) : 0.f;
+        const float sum = warp_sum(pj);
+        if (lane < k) {
+            top_idx[(size_t)t * k + lane] = chosen_e;
+            top_w[(size_t)t * k + lane] = pj / sum;
+        }
     }
 }
 
 // ------------------------------------------------------------------ pairs sorted by expert
 // One block.  sorted[cap]: the pairs of expert 0, padded with -1 to a multiple of BM, then those of expert
-// 1, ...; tile_expert[i]: the expert of tile i; *n_tiles: the tiles in use.
+// 1, ...; tile_expert[i]: the expert of tile i; *n_tiles: the tiles in use; place[i] (may be null): where pair
+// i stands in `sorted`.
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ top_idx, int n_pairs, int E, int BM,
                                                          int cap, int* __restrict__ sorted, int* __restrict__ tile_expert,
-                                                         int* __restrict__ n_tiles) {
+                                                         int* __restrict__ n_tiles, int* __restrict__ place) {
     __shared__ int cnt[1024], off[1025];
     const int tid = threadIdx.x;
     for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
@@ -116,6 +170,9 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
         if (e >= 0 && e < E) {
             const int at = off[e] + atomicAdd(&cnt[e], 1);
             if (at < cap) sorted[at] = i;
+            if (place != nullptr) place[i] = at < cap ? at : -1;
+        } else if (place != nullptr) {
+            place[i] = -1;
         }
     }
 }
@@ -316,18 +373,38 @@ __global__ void __launch_bounds__(256) moe_gemm_plain_kernel(MoeGemm p) {
     }
 }
 
-// y[t] = sum_j pair_out[t * k + j]  (+ gate[t] * shared[t]), float32.
+// y[t] = sum_j w_j * pair_out[row_j]  (+ gate[t] * shared[t]), float32, with row_j = place[t * k + j] (null:
+// t * k + j) and w_j = weight[t * k + j] (null: 1, the rows are weighted already).
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, int k, const T* __restrict__ shared,
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, int k, const int* __restrict__ place,
+                                   const float* __restrict__ weight, const T* __restrict__ shared,
                                    const float* __restrict__ gate, float* __restrict__ y, int D) {
     const size_t t = blockIdx.x;
     const float gt = shared != nullptr ? gate[t] : 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float s = 0.f;
-        for (int j = 0; j < k; ++j) s += pair_out[(t * k + j) * D + c];
+        for (int j = 0; j < k; ++j) {
+            const long long row = place != nullptr ? place[t * k + j] : (long long)(t * k + j);
+            if (row < 0) continue;
+            const float v = pair_out[(size_t)row * D + c];
+            s = weight != nullptr ? fmaf(weight[t * k + j], v, s) : s + v;
+        }
         if (shared != nullptr) s = fmaf(gt, to_float(shared[t * D + c]), s);
         y[t * D + c] = s;
     }
+}
+
+// out[i] = A[sorted[i] / a_div] (zeros where sorted[i] < 0): the left operand of the experts' first product in
+// the order of `sorted`, for the tensor-core form that reads its tiles with TMA.  16-byte chunks.
+__global__ void moe_gather_kernel(const uint4* __restrict__ A, int row_chunks, int a_div, const int* __restrict__ sorted,
+                                  const int* __restrict__ n_tiles, int BM, int n_pairs, uint4* __restrict__ out) {
+    const int i = blockIdx.x;
+    if (i >= *n_tiles * BM) return;
+    const int id = sorted[i];
+    const bool ok = id >= 0 && id < n_pairs;
+    const uint4* src = A + (size_t)(ok ? id / a_div : 0) * row_chunks;
+    uint4* dst = out + (size_t)i * row_chunks;
+    for (int c = threadIdx.x; c < row_chunks; c += blockDim.x) dst[c] = ok ? src[c] : make_uint4(0, 0, 0, 0);
 }
 
 template <int BM, bool GATED>
@@ -353,14 +430,16 @@ PL_EXPORT int pl_moe_route(const void* h, int ldh, const void* W, int dtype, int
     if (tokens == 0) return 0;
     PL_REQUIRE(tokens > 0 && D > 0 && E > 0 && k > 0 && k <= E && k <= 32 && E <= 1024,
                "moe_route: tokens=%d width=%d experts=%d top=%d (top <= 32, experts <= 1024)", tokens, D, E, k);
-    const size_t smem = (size_t)4 * (E + 1) * sizeof(float);
-    const dim3 grid((tokens + 3) / 4);
+    const size_t smem = (size_t)RT_TOK * (E + 1) * sizeof(float);
+    const dim3 grid((tokens + RT_TOK - 1) / RT_TOK);
+    const int per16 = dtype == PL_F32 ? 4 : 8;
+    const int vec = D % per16 == 0 && ldh % per16 == 0 && (((uintptr_t)h | (uintptr_t)W) & 15) == 0;
     if (dtype == PL_F32)
-        moe_route_kernel<float><<<grid, 128, smem, stream>>>((const float*)h, ldh, (const float*)W, tokens, D, E, k,
-                                                              shared_gate, top_idx, top_w, gate);
+        moe_route_kernel<float><<<grid, RT_WARPS * 32, smem, stream>>>((const float*)h, ldh, (const float*)W, tokens, D, E, k,
+                                                                        shared_gate, vec, top_idx, top_w, gate);
     else if (dtype == PL_BF16)
-        moe_route_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)W,
-                                                                      tokens, D, E, k, shared_gate, top_idx, top_w, gate);
+        moe_route_kernel<__nv_bfloat16><<<grid, RT_WARPS * 32, smem, stream>>>(
+            (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)W, tokens, D, E, k, shared_gate, vec, top_idx, top_w, gate);
     else
         return pl_fail("moe_route: unknown dtype %d", dtype);
     PL_LAUNCHED("moe_route");
@@ -368,11 +447,21 @@ PL_EXPORT int pl_moe_route(const void* h, int ldh, const void* W, int dtype, int
 }
 
 PL_EXPORT int pl_moe_align(const int* top_idx, int n_pairs, int E, int BM, int cap, int* sorted, int* tile_expert,
-                           int* n_tiles, cudaStream_t stream) {
-    PL_REQUIRE(n_pairs > 0 && E > 0 && E <= 1024 && (BM == 16 || BM == 64) && cap % BM == 0,
+                           int* n_tiles, int* place, cudaStream_t stream) {
+    PL_REQUIRE(n_pairs > 0 && E > 0 && E <= 1024 && (BM == 16 || BM == 64 || BM == 256) && cap % BM == 0,
                "moe_align: pairs=%d experts=%d BM=%d cap=%d", n_pairs, E, BM, cap);
-    moe_align_kernel<<<1, 1024, 0, stream>>>(top_idx, n_pairs, E, BM, cap, sorted, tile_expert, n_tiles);
+    moe_align_kernel<<<1, 1024, 0, stream>>>(top_idx, n_pairs, E, BM, cap, sorted, tile_expert, n_tiles, place);
     PL_LAUNCHED("moe_align");
+    return 0;
+}
+
+// out[cap][K] (bfloat16) = rows of A in the order of `sorted`; K a multiple of 8, both 16-byte aligned.
+PL_EXPORT int pl_moe_gather(const void* A, int lda, int a_div, const int* sorted, const int* n_tiles, int BM, int cap,
+                            int n_pairs, int K, void* out, cudaStream_t stream) {
+    PL_REQUIRE(cap > 0 && K > 0 && K % 8 == 0 && lda == K && a_div > 0 && (((uintptr_t)A | (uintptr_t)out) & 15) == 0,
+               "moe_gather: cap=%d K=%d lda=%d", cap, K, lda);
+    moe_gather_kernel<<<cap, 128, 0, stream>>>((const uint4*)A, K / 8, a_div, sorted, n_tiles, BM, n_pairs, (uint4*)out);
+    PL_LAUNCHED("moe_gather");
     return 0;
 }
 
@@ -407,15 +496,16 @@ PL_EXPORT int pl_moe_gemm(const void* A, int lda, int a_div, const void* W, void
     return 0;
 }
 
-PL_EXPORT int pl_moe_combine(const float* pair_out, int k, const void* shared, int shared_dtype, const float* gate,
-                             float* y, int tokens, int D, cudaStream_t stream) {
+PL_EXPORT int pl_moe_combine(const float* pair_out, int k, const int* place, const float* weight, const void* shared,
+                             int shared_dtype, const float* gate, float* y, int tokens, int D, cudaStream_t stream) {
     if (tokens == 0) return 0;
     PL_REQUIRE(tokens > 0 && D > 0 && k > 0, "moe_combine: bad sizes");
     const int threads = D >= 1024 ? 256 : 128;
     if (shared == nullptr || shared_dtype == PL_F32)
-        moe_combine_kernel<float><<<tokens, threads, 0, stream>>>(pair_out, k, (const float*)shared, gate, y, D);
+        moe_combine_kernel<float><<<tokens, threads, 0, stream>>>(pair_out, k, place, weight, (const float*)shared, gate, y, D);
     else if (shared_dtype == PL_BF16)
-        moe_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(pair_out, k, (const __nv_bfloat16*)shared, gate, y, D);
+        moe_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(pair_out, k, place, weight,
+                                                                          (const __nv_bfloat16*)shared, gate, y, D);
     else
         return pl_fail("moe_combine: unknown dtype %d", shared_dtype);
     PL_LAUNCHED("moe_combine");

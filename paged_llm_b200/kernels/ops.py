@@ -122,8 +122,10 @@ class CudaOps:
         # "" for none) to run on it from 129 tokens on instead.
         tc_for = os.environ.get("PAGED_LLM_B200_GEMM_TC")
         self.gemm_tc_min_tokens = 2048 if tc_for is None else 129
-        tc_for = "silu" if tc_for is None else tc_for
-        self.gemm_tc_for = {"silu", "add", "plain"} if tc_for == "all" else {t for t in tc_for.split(",") if t}
+        tc_for = "silu,moe" if tc_for is None else tc_for
+        self.gemm_tc_for = {"silu", "add", "plain", "moe"} if tc_for == "all" else {t for t in tc_for.split(",") if t}
+        # (token, expert) pairs of a step from which the routed experts' products take the grouped tcgen05 form
+        self.moe_tc_min_pairs = 2048
         self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
         # decode steps of more than 16 tokens: rotary positions and the cache write inside the attention kernel
         self.rope_in_attention = os.environ.get("PAGED_LLM_B200_NO_ROPE_IN_ATTENTION") is None
@@ -374,9 +376,14 @@ class CudaOps:
             self.launches += 1
             return out
         h = self.materialize(h)
-        if activation == "silu" and self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
+        if self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
             out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
-            self._gemm_tc(h, w_gate_up, out, None, I, 2)
+            if activation == "silu":
+                self._gemm_tc(h, w_gate_up, out, None, I, 2)
+            else:
+                _check(self.core, self.core.pl_gemm_tc_act(self._p(h), h.stride(0), self._p(w_gate_up), self._p(out), I, M, I,
+                                                           K, ACTIVATIONS[activation], self._stream))
+                self.launches += 1
             return out
         return self.act_mul(self.linear(h, w_gate_up), activation)
 
@@ -418,7 +425,8 @@ class CudaOps:
         [D, Fs]) or None.  Router logits, top-k, the softmax over the chosen logits and the final weighted
         sum are float32.  Kernels: router; (token, choice) pairs sorted by expert on the device; the
         experts' two products over tiles of that list (bfloat16: mma.sync tiles of 64 pairs, or of 16 when
-        experts get few pairs as in decoding; float32 and odd sizes: FFMA chains in k order); the sum.
+        experts get few pairs as in decoding, or, with many pairs per expert, the grouped form of the tcgen05
+        product over rows gathered in sorted order; float32 and odd sizes: FFMA chains in k order); the sum.
         Nothing is read back, so the step can be captured."""
         h = self.materialize(h)
         assert h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_router.is_contiguous()
@@ -436,28 +444,47 @@ class CudaOps:
         _check(lib, lib.pl_moe_route(self._p(h), D, self._p(w_router), code, T, D, E, top_k, 1 if shared is not None else 0,
                                      self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
         tensor_cores = h.dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
-        BM = 64 if tensor_cores and pairs >= 32 * E else 16
+        # Many pairs per expert (prompt portions): the experts' products run on the tcgen05 kernel of the dense
+        # layers in its grouped form, over rows gathered in the order of the sorted list (tiles of 256 pairs).
+        grouped_tc = (tensor_cores and "moe" in self.gemm_tc_for and D % 64 == 0 and F % 64 == 0
+                      and pairs >= max(self.moe_tc_min_pairs, 96 * E))
+        BM = 256 if grouped_tc else (64 if tensor_cores and pairs >= 32 * E else 16)
         max_tiles = pairs // BM + min(pairs, E)
-        sorted_pairs = torch.empty(max_tiles * BM, dtype=torch.int32, device=dev)
+        cap = max_tiles * BM
+        sorted_pairs = torch.empty(cap, dtype=torch.int32, device=dev)
         tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
         n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-        _check(lib, lib.pl_moe_align(self._p(top_idx), pairs, E, BM, max_tiles * BM, self._p(sorted_pairs),
-                                     self._p(tile_expert), self._p(n_tiles), self._stream))
-        inter = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        place = torch.empty(pairs, dtype=torch.int32, device=dev) if grouped_tc else None
+        _check(lib, lib.pl_moe_align(self._p(top_idx), pairs, E, BM, cap, self._p(sorted_pairs),
+                                     self._p(tile_expert), self._p(n_tiles), self._p(place), self._stream))
         act = ACTIVATIONS[activation]
-        _check(lib, lib.pl_moe_gemm(self._p(h), D, top_k, self._p(w_gate_up), self._p(inter), F, self._p(sorted_pairs),
-                                    self._p(tile_expert), self._p(n_tiles), c_void_p(0), pairs, F, D, 1, act, code, BM,
-                                    max_tiles, 1 if tensor_cores else 0, self._stream))
-        pair_out = torch.empty((pairs, D), dtype=torch.float32, device=dev)
-        _check(lib, lib.pl_moe_gemm(self._p(inter), F, 1, self._p(w_down), self._p(pair_out), D, self._p(sorted_pairs),
-                                    self._p(tile_expert), self._p(n_tiles), self._p(top_w), pairs, D, F, 0, act, code, BM,
-                                    max_tiles, 1 if tensor_cores else 0, self._stream))
-        self.launches += 4
+        if grouped_tc:
+            xs = torch.empty((cap, D), dtype=h.dtype, device=dev)
+            _check(lib, lib.pl_moe_gather(self._p(h), D, top_k, self._p(sorted_pairs), self._p(n_tiles), BM, cap, pairs, D,
+                                          self._p(xs), self._stream))
+            inter = torch.empty((cap, F), dtype=h.dtype, device=dev)
+            _check(self.core, self.core.pl_gemm_tc_grouped(self._p(xs), D, self._p(w_gate_up), self._p(inter), F, cap, F, D,
+                                                           2, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
+            pair_out = torch.empty((cap, D), dtype=torch.float32, device=dev)
+            _check(self.core, self.core.pl_gemm_tc_grouped(self._p(inter), F, self._p(w_down), self._p(pair_out), D, cap, D, F,
+                                                           1, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
+            self.launches += 5
+        else:
+            inter = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+            _check(lib, lib.pl_moe_gemm(self._p(h), D, top_k, self._p(w_gate_up), self._p(inter), F, self._p(sorted_pairs),
+                                        self._p(tile_expert), self._p(n_tiles), c_void_p(0), pairs, F, D, 1, act, code, BM,
+                                        max_tiles, 1 if tensor_cores else 0, self._stream))
+            pair_out = torch.empty((pairs, D), dtype=torch.float32, device=dev)
+            _check(lib, lib.pl_moe_gemm(self._p(inter), F, 1, self._p(w_down), self._p(pair_out), D, self._p(sorted_pairs),
+                                        self._p(tile_expert), self._p(n_tiles), self._p(top_w), pairs, D, F, 0, act, code, BM,
+                                        max_tiles, 1 if tensor_cores else 0, self._stream))
+            self.launches += 4
         s = None
         if shared is not None:
             s = self.linear(self.gated_act_linear(h, shared[0], shared_activation), shared[1])
         y = torch.empty((T, D), dtype=torch.float32, device=dev)
-        _check(lib, lib.pl_moe_combine(self._p(pair_out), top_k, self._p(s), self._code(s) if s is not None else PL_F32,
+        _check(lib, lib.pl_moe_combine(self._p(pair_out), top_k, self._p(place), self._p(top_w) if grouped_tc else c_void_p(0),
+                                       self._p(s), self._code(s) if s is not None else PL_F32,
                                        self._p(gate), self._p(y), T, D, self._stream))
         self.launches += 1
         return y

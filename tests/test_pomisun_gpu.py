@@ -327,6 +327,61 @@ def test_routed_experts(ops, dtype, T, D, E, k, F, shared):
     torch.testing.assert_close(got.double().cpu(), want, atol=tol(dtype, scale), rtol=tol(dtype))
 
 
+@pytest.mark.parametrize("T,D,E,k,F,shared", [(1100, 128, 4, 2, 64, 32), (700, 192, 6, 3, 128, None), (2048, 256, 16, 1, 64, 64)])
+def test_routed_experts_on_the_grouped_tensor_core_product(ops, T, D, E, k, F, shared):
+    """Many pairs per expert: the experts' products run on the tcgen05 kernel in its grouped form (rows gathered
+    in sorted order, tiles of 256 pairs of one expert, the count of tiles read on the device); one expert gets
+    no token at all."""
+    ops.set_compute_dtype(torch.bfloat16)
+    w = {"m.router": randn(E, D, seed=1, dtype=torch.bfloat16, std=1.0)}
+    w["m.router"][E - 1] = 0
+    w["m.router"][E - 1, 0] = -100.0                         # never chosen (the inputs' first column is positive)
+    for e in range(E):
+        w[f"m.e{e}.gate"] = randn(F, D, seed=10 + e, dtype=torch.bfloat16, std=D ** -0.5)
+        w[f"m.e{e}.up"] = randn(F, D, seed=100 + e, dtype=torch.bfloat16, std=D ** -0.5)
+        w[f"m.e{e}.down"] = randn(D, F, seed=1000 + e, dtype=torch.bfloat16, std=F ** -0.5)
+    mlp = {"router": {"experts": E, "top": k}}
+    if shared:
+        mlp["shared"] = {"ff": shared}
+        w["m.shared.gate"] = randn(shared, D, seed=5, dtype=torch.bfloat16, std=D ** -0.5)
+        w["m.shared.up"] = randn(shared, D, seed=6, dtype=torch.bfloat16, std=D ** -0.5)
+        w["m.shared.down"] = randn(D, shared, seed=7, dtype=torch.bfloat16, std=shared ** -0.5)
+        w["m.shared.sg"] = randn(1, D, seed=8, dtype=torch.bfloat16, std=0.3)
+    h = randn(T, D, seed=9, dtype=torch.bfloat16)
+    h[:, 0] = h[:, 0].abs() + 1
+    want = plain_pomisun.routed(h.double(), mlp, {n: t.double() for n, t in w.items()}, "m.")
+    from paged_llm_b200.parts.routed_mlp import RoutedMLP
+    part = RoutedMLP({n[2:]: n for n in w}, hidden_size=D, expert_size=F, num_experts=E, top_k=k, shared_size=shared)
+    part.load({n: t.cuda() for n, t in w.items()})
+    old = ops.moe_tc_min_pairs
+    try:
+        launches = []
+        for least in (1024, 1 << 30):                        # the grouped form, then the mma.sync tiles
+            ops.moe_tc_min_pairs = least
+            before = ops.launches
+            got = part.forward(h.cuda(), types.SimpleNamespace(ops=ops))
+            launches.append(ops.launches - before)
+            ops.check_kernels()
+            scale = float(want.abs().max())
+            torch.testing.assert_close(got.double().cpu(), want, atol=1.6e-2 * scale, rtol=1.6e-2)
+        assert launches[0] == launches[1] + 1, "the grouped form (one more kernel: the gather) was not taken"
+    finally:
+        ops.moe_tc_min_pairs = old
+
+
+@pytest.mark.parametrize("M,I,K", [(2048, 256, 128), (2100, 200, 192)])
+def test_many_token_product_with_the_gelu_gate(ops, M, I, K):
+    """From 2,048 tokens on the gate/up product runs on the tcgen05 kernel with the activation in its epilogue."""
+    ops.set_compute_dtype(torch.bfloat16)
+    h = randn(M, K, seed=1, dtype=torch.bfloat16)
+    w = randn(2 * I, K, seed=2, dtype=torch.bfloat16, std=K ** -0.5)
+    got = ops.gated_act_linear(h.cuda(), w.cuda(), "gelu_tanh").double().cpu()
+    ops.check_kernels()
+    z = (h.double() @ w.double().T).to(torch.bfloat16).double()
+    want = plain_pomisun.gelu_tanh(z[:, :I]) * z[:, I:]
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+
+
 def test_router_weights_are_a_softmax_over_the_chosen(ops):
     """One expert far ahead, the others level: its weight is e^a / (e^a + (k - 1)), not a share of all experts."""
     ops.set_compute_dtype(torch.float32)
