@@ -1,7 +1,8 @@
 // A feed-forward of routed experts: router, the list of (token, expert) pairs sorted by expert, the
 // experts' products over that list, and the weighted sum.
 //
-//   z = W_r h (float32);  the k largest z choose the experts;  their weights are the softmax over those k;
+//   z = W_r h (float32, a product of the kernel library);  the k largest z choose the experts;  their weights
+//   are the softmax over those k;
 //   y = sum_j weight_j * down_e(j)(act(gate_e(j) h) * up_e(j) h)  [+ sigmoid(w_s . h) * shared(h)]
 //
 // Nothing here looks at the batch on the host: the counts per expert stay on the device, every kernel is
@@ -16,120 +17,58 @@ namespace {
 
 __device__ __forceinline__ float act_f(int act, float z) { return act == 1 ? gelu_tanh_f(z) : silu_f(z); }
 
-// ------------------------------------------------------------------ router
-// A block of 8 warps takes RT_TOK tokens.  logits[t][e] = sum_c h[t][c] * W[e][c] in float32 for the E experts
-// and, if `shared_gate`, one more row of W whose sigmoid is the token's factor for the shared expert: the
-// warps share the rows of W between them, a lane reads 16 bytes of a row once and multiplies them into all
-// the block's tokens (whose rows stay in L1).  Then warp t picks the k largest of token t, one after the
-// other (among equals the lowest index), and forms the softmax over the chosen.
-constexpr int RT_TOK = 8, RT_WARPS = 8;
-
-template <typename T> struct Ld16 {};
-template <> struct Ld16<float> {
-    static constexpr int N = 4;
-    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
-        const float4 a = *reinterpret_cast<const float4*>(p);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    }
-};
-template <> struct Ld16<__nv_bfloat16> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(p);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[2 * i] = __low2float(h2[i]);
-            v[2 * i + 1] = __high2float(h2[i]);
-        }
-    }
-};
-
-template <typename T>
-__global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ W,
-                                                                  int tokens, int D, int E, int k, int shared_gate, int vec,
-                                                                  int* __restrict__ top_idx, float* __restrict__ top_w,
-                                                                  float* __restrict__ gate) {
-    extern __shared__ float z_all[];                    // [RT_TOK][E + 1]
+// ------------------------------------------------------------------ the router's choice
+// The logits z[t][0..E) (and, if `shared_gate`, z[t][E], whose sigmoid is the token's factor for the shared
+// expert) come from a product of the kernel library in float32.  One warp per token picks the k largest, one
+// after the other (among equals the lowest index), and forms the softmax over the chosen.
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ z_all, int ldz, int tokens, int E, int k,
+                                                       int shared_gate, int* __restrict__ top_idx,
+                                                       float* __restrict__ top_w, float* __restrict__ gate) {
+    extern __shared__ float z_smem[];                   // [4][E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * RT_TOK;
-    const int nt = min(RT_TOK, tokens - t0);
-    const int rows = E + (shared_gate ? 1 : 0);
-    constexpr int N = Ld16<T>::N;
-    for (int e = warp; e < rows; e += RT_WARPS) {
-        const T* w = W + (size_t)e * D;
-        float acc[RT_TOK];
-#pragma unroll
-        for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
-        if (vec) {
-            for (int c = lane * N; c < D; c += 32 * N) {
-                float wv[8], xv[8];
-                Ld16<T>::load(w + c, wv);
-#pragma unroll
-                for (int t = 0; t < RT_TOK; ++t) {
-                    if (t < nt) {
-                        Ld16<T>::load(h + (size_t)(t0 + t) * ldh + c, xv);
-#pragma unroll
-                        for (int i = 0; i < N; ++i) acc[t] = fmaf(xv[i], wv[i], acc[t]);
-                    }
-                }
-            }
-        } else {
-            for (int c = lane; c < D; c += 32) {
-                const float wv = to_float(w[c]);
-#pragma unroll
-                for (int t = 0; t < RT_TOK; ++t)
-                    if (t < nt) acc[t] = fmaf(to_float(h[(size_t)(t0 + t) * ldh + c]), wv, acc[t]);
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    float* z = z_smem + warp * E;
+    const float* src = z_all + (size_t)t * ldz;
+    for (int e = lane; e < E; e += 32) z[e] = src[e];
+    if (shared_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-src[E]));
+    __syncwarp();
+    float chosen_z = 0.f, z_max = 0.f;
+    int chosen_e = -1;                                  // lane j keeps choice j (k <= 32)
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < arg)) {
+                best = v;
+                arg = e;
             }
         }
 #pragma unroll
-        for (int t = 0; t < RT_TOK; ++t) {
-            const float s = warp_sum(acc[t]);
-            if (lane == 0) z_all[t * (E + 1) + e] = s;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
         }
+        if (arg >= E) arg = 0;                          // (only if every logit left is NaN)
+        if (j == 0) z_max = best;
+        if (lane == j) {
+            chosen_z = best;
+            chosen_e = arg;
+        }
+        __syncwarp();
+        if (lane == 0) z[arg] = -INFINITY;
+        __syncwarp();
     }
-    __syncthreads();
-    for (int tl = warp; tl < nt; tl += RT_WARPS) {
-        const int t = t0 + tl;
-        float* z = z_all + tl * (E + 1);
-        if (shared_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
-        float chosen_z = 0.f, z_max = 0.f;
-        int chosen_e = -1;                                  // lane j keeps choice j (k <= 32)
-        for (int j = 0; j < k; ++j) {
-            float best = -INFINITY;
-            int arg = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const float v = z[e];
-                if (v > best || (v == best && e < arg)) {
-                    best = v;
-                    arg = e;
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-                if (ob > best || (ob == best && oa < arg)) {
-                    best = ob;
-                    arg = oa;
-                }
-            }
-            if (arg >= E) arg = 0;                          // (only if every logit left is NaN)
-            if (j == 0) z_max = best;
-            if (lane == j) {
-                chosen_z = best;
-                chosen_e = arg;
-            }
-            __syncwarp();
-            if (lane == 0) z[arg] = -INFINITY;
-            __syncwarp();
-        }
-        const float pj = lane < k ? expf(chosen_z - z_max) : 0.f;
-        const float sum = warp_sum(pj);
-        if (lane < k) {
-            top_idx[(size_t)t * k + lane] = chosen_e;
-            top_w[(size_t)t * k + lane] = pj / sum;
-        }
+    const float pj = lane < k ? expf(chosen_z - z_max) : 0.f;
+    const float sum = warp_sum(pj);
+    if (lane < k) {
+        top_idx[(size_t)t * k + lane] = chosen_e;
+        top_w[(size_t)t * k + lane] = pj / sum;
     }
 }
 
@@ -425,24 +364,14 @@ int launch_moe_bf16(const MoeGemm& p, int max_tiles, cudaStream_t stream) {
 
 }  // namespace
 
-PL_EXPORT int pl_moe_route(const void* h, int ldh, const void* W, int dtype, int tokens, int D, int E, int k,
-                           int shared_gate, int* top_idx, float* top_w, float* gate, cudaStream_t stream) {
+PL_EXPORT int pl_moe_topk(const float* z, int ldz, int tokens, int E, int k, int shared_gate, int* top_idx, float* top_w,
+                          float* gate, cudaStream_t stream) {
     if (tokens == 0) return 0;
-    PL_REQUIRE(tokens > 0 && D > 0 && E > 0 && k > 0 && k <= E && k <= 32 && E <= 1024,
-               "moe_route: tokens=%d width=%d experts=%d top=%d (top <= 32, experts <= 1024)", tokens, D, E, k);
-    const size_t smem = (size_t)RT_TOK * (E + 1) * sizeof(float);
-    const dim3 grid((tokens + RT_TOK - 1) / RT_TOK);
-    const int per16 = dtype == PL_F32 ? 4 : 8;
-    const int vec = D % per16 == 0 && ldh % per16 == 0 && (((uintptr_t)h | (uintptr_t)W) & 15) == 0;
-    if (dtype == PL_F32)
-        moe_route_kernel<float><<<grid, RT_WARPS * 32, smem, stream>>>((const float*)h, ldh, (const float*)W, tokens, D, E, k,
-                                                                        shared_gate, vec, top_idx, top_w, gate);
-    else if (dtype == PL_BF16)
-        moe_route_kernel<__nv_bfloat16><<<grid, RT_WARPS * 32, smem, stream>>>(
-            (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)W, tokens, D, E, k, shared_gate, vec, top_idx, top_w, gate);
-    else
-        return pl_fail("moe_route: unknown dtype %d", dtype);
-    PL_LAUNCHED("moe_route");
+    PL_REQUIRE(tokens > 0 && E > 0 && k > 0 && k <= E && k <= 32 && E <= 1024 && ldz >= E + (shared_gate ? 1 : 0),
+               "moe_topk: tokens=%d experts=%d top=%d (top <= 32, experts <= 1024)", tokens, E, k);
+    moe_topk_kernel<<<(tokens + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(z, ldz, tokens, E, k, shared_gate, top_idx,
+                                                                                   top_w, gate);
+    PL_LAUNCHED("moe_topk");
     return 0;
 }
 

@@ -423,7 +423,7 @@ class CudaOps:
         w_router [E (+1), D]: the router's rows and, with a shared expert, the row of its gate; w_gate_up
         [E, 2F, D] (gate rows over up rows) and w_down [E, D, F]; `shared` = (gate over up [2Fs, D], down
         [D, Fs]) or None.  Router logits, top-k, the softmax over the chosen logits and the final weighted
-        sum are float32.  Kernels: router; (token, choice) pairs sorted by expert on the device; the
+        sum are float32.  Kernels: the router's product and choice; (token, choice) pairs sorted by expert on the device; the
         experts' two products over tiles of that list (bfloat16: mma.sync tiles of 64 pairs, or of 16 when
         experts get few pairs as in decoding, or, with many pairs per expert, the grouped form of the tcgen05
         product over rows gathered in sorted order; float32 and odd sizes: FFMA chains in k order); the sum.
@@ -441,8 +441,9 @@ class CudaOps:
         top_idx = torch.empty(pairs, dtype=torch.int32, device=dev)
         top_w = torch.empty(pairs, dtype=torch.float32, device=dev)
         gate = torch.empty(T, dtype=torch.float32, device=dev) if shared is not None else None
-        _check(lib, lib.pl_moe_route(self._p(h), D, self._p(w_router), code, T, D, E, top_k, 1 if shared is not None else 0,
-                                     self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
+        z = self.linear(h, w_router, out_float32=True)          # float32 logits (and the shared expert's gate)
+        _check(lib, lib.pl_moe_topk(self._p(z), z.shape[1], T, E, top_k, 1 if shared is not None else 0,
+                                    self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
         tensor_cores = h.dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
         # Many pairs per expert (prompt portions): the experts' products run on the tcgen05 kernel of the dense
         # layers in its grouped form, over rows gathered in the order of the sorted list (tiles of 256 pairs).
