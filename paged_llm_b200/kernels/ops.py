@@ -420,7 +420,8 @@ class CudaOps:
                        shared_activation: str = "silu") -> torch.Tensor:
         """The feed-forward of routed experts for the step's tokens: float32 [T, D].
 
-        w_router [E (+1), D]: the router's rows and, with a shared expert, the row of its gate; w_gate_up
+        w_router [E (+1) or more, D]: the router's rows and, with a shared expert, the row of its gate (further rows
+        are ignored); w_gate_up
         [E, 2F, D] (gate rows over up rows) and w_down [E, D, F]; `shared` = (gate over up [2Fs, D], down
         [D, Fs]) or None.  Router logits, top-k, the softmax over the chosen logits and the final weighted
         sum are float32.  Kernels: the router's product and choice; (token, choice) pairs sorted by expert on the device; the
@@ -433,7 +434,7 @@ class CudaOps:
         T, D = h.shape
         E, F2, _ = w_gate_up.shape
         F = F2 // 2
-        assert w_down.shape == (E, D, F) and w_router.shape == (E + (1 if shared is not None else 0), D)
+        assert w_down.shape == (E, D, F) and w_router.shape[0] >= E + (1 if shared is not None else 0) and w_router.shape[1] == D
         assert w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype and w_router.dtype == h.dtype
         lib = load_module("moe")
         dev, code = self.device, self._code(h)

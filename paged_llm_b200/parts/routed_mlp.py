@@ -31,7 +31,7 @@ class RoutedMLP(FeedForward):
         self.activation, self.shared_size = activation, shared_size
         self.shared_activation = shared_activation or activation
         self.names = weights
-        self.w_router = None          # [E (+1), D]: the router's rows, then the shared expert's gate
+        self.w_router = None          # [E (+1) and padding, D]: the router's rows, then the shared expert's gate
         self.w_gate_up = None         # [E, 2F, D]
         self.w_down = None            # [E, D, F]
         self.shared = None            # (gate over up [2Fs, D], down [D, Fs])
@@ -60,6 +60,10 @@ class RoutedMLP(FeedForward):
             router.append(t[n["shared.sg"]])
             self.shared = (torch.cat([t[n["shared.gate"]], t[n["shared.up"]]], dim=0).contiguous(),
                            t[n["shared.down"]].contiguous())
+        rows = sum(r.shape[0] for r in router)
+        if rows % 8:
+            # rows of zeros up to a multiple of 8: the library's product of the logits then takes an aligned form
+            router.append(torch.zeros((8 - rows % 8, self.hidden_size), dtype=router[0].dtype, device=router[0].device))
         self.w_router = torch.cat(router, dim=0).contiguous()
 
     def bytes_read_per_step(self):

@@ -72,7 +72,7 @@ class TorchOps:
                        shared_activation="silu"):
         self._count("routed_experts")
         E = w_gate_up.shape[0]
-        z = h.float() @ w_router.float().T
+        z = h.float() @ w_router.float().T              # (rows behind the experts' and the gate's are padding)
         top, idx = torch.topk(z[:, :E], top_k, dim=-1)
         wt = torch.softmax(top, dim=-1)
         y = torch.zeros(h.shape[0], w_down.shape[1], dtype=torch.float32, device=h.device)
