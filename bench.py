@@ -565,9 +565,9 @@ def pomisun_configs(name: str):
     """(Pomisun configuration dict, Llama configuration dict of equal size, number of layer runs)."""
     s = POMISUN_SIZES[name]
     mixer = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
-             "softcap": 50.0, "mask": {"size": s["chunk"]},
-             "rot": {"dims": s["dim"], "base": 1000000.0,
-                     "scaling": {"factor": 2.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+             "softcap": 30.0, "mask": {"size": s["chunk"]},
+             "rot": {"dims": s["dim"], "base": 500000.0,
+                     "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     dense = {"kind": "dense", "ff": s["ff"]}
     moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]},
            "shared": {"ff": s["shared_ff"]}}
@@ -579,7 +579,7 @@ def pomisun_configs(name: str):
         runs += (s["loop"]["stop"] - s["loop"]["start"]) * (s["loop"]["times"] - 1)
     llama = {"architectures": ["LlamaForCausalLM"], "vocab_size": s["vocab"], "hidden_size": s["width"],
              "intermediate_size": s["ff"], "num_hidden_layers": runs, "num_attention_heads": s["heads"],
-             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 500000.0, "rms_norm_eps": 1e-6,
              "tie_word_embeddings": True, "max_position_embeddings": 8192}
     return pom, llama, runs
 

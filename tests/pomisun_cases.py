@@ -64,9 +64,9 @@ CASE_Q = {
 CASE_R = {
     "architecture": "Pomisun", "vocab": 300, "width": 128, "norm": {"eps": 1e-6},
     "layers": [
-        _layer(_attn(2, 1, 64, rot={"dims": 64, "base": 1000000.0, "scaling": dict(YARN, original=128)}),
+        _layer(_attn(2, 1, 64, rot={"dims": 64, "base": 250000.0, "scaling": dict(YARN, original=128)}),
                {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 8, "top": 1}, "shared": {"ff": 32}}),
-        _layer(_attn(4, 1, 64, chunk=32, rot={"dims": 64, "base": 1000000.0, "scaling": dict(YARN, original=128)}),
+        _layer(_attn(4, 1, 64, chunk=32, rot={"dims": 64, "base": 250000.0, "scaling": dict(YARN, original=128)}),
                {"kind": "dense", "ff": 160}),
     ],
 }

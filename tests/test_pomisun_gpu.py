@@ -107,7 +107,7 @@ def plain_rows(q_rows, keys, vals, nq, L, scale, softcap, chunk):
 # ---------------------------------------------------------------- the chunked mask
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("softcap", [None, 4.0])
-@pytest.mark.parametrize("nh,nkv,d,chunk,ps", [(4, 2, 16, 24, 8), (8, 1, 96, 96, 16), (6, 3, 32, 40, 16), (4, 1, 64, 32, 16),
+@pytest.mark.parametrize("nh,nkv,d,chunk,ps", [(4, 2, 16, 24, 8), (10, 2, 96, 80, 16), (6, 3, 32, 40, 16), (4, 1, 64, 32, 16),
                                               (2, 2, 128, 50, 32), (32, 1, 48, 7, 16)])
 def test_chunked_attention(ops, dtype, softcap, nh, nkv, d, chunk, ps):
     """Prompt portions that start and end anywhere in a chunk beside decoded tokens just before, at and just
@@ -165,11 +165,11 @@ def test_keys_at_the_edge_of_a_chunk(ops, dtype, decoded):
 def test_one_far_chunk_among_many(ops):
     """Decoding far into a long request: of 4,000 keys only those of the last chunk count, whatever the splits."""
     ops.set_compute_dtype(torch.bfloat16)
-    nh, nkv, d, ps, chunk = 8, 1, 96, 16, 96
-    for L in (4000, 3937, 3936 + 96):
+    nh, nkv, d, ps, chunk = 12, 3, 80, 16, 112
+    for L in (4000, 3921, 3920 + 112):
         q, kv, bt, keys, vals = paged_case([1], [L], nh, nkv, d, ps, torch.bfloat16, seed=L)
-        out, _ = run_attention(ops, q, kv, bt, [1], [L], nh, nkv, d, torch.bfloat16, d ** -0.5, chunk, 50.0)
-        want = plain_rows(q, keys[0], vals[0], 1, L, d ** -0.5, 50.0, chunk)
+        out, _ = run_attention(ops, q, kv, bt, [1], [L], nh, nkv, d, torch.bfloat16, d ** -0.5, chunk, 20.0)
+        want = plain_rows(q, keys[0], vals[0], 1, L, d ** -0.5, 20.0, chunk)
         torch.testing.assert_close(out, want, atol=1.6e-2, rtol=1.6e-2)
 
 
@@ -187,7 +187,7 @@ def test_rotary_table_with_yarn(ops):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,d,rd", [(4, 2, 16, 16), (8, 1, 96, 96), (6, 3, 32, 16), (3, 1, 48, 8), (2, 2, 64, 64)])
+@pytest.mark.parametrize("nh,nkv,d,rd", [(4, 2, 16, 16), (5, 1, 96, 96), (6, 3, 32, 16), (3, 1, 48, 8), (2, 2, 64, 64)])
 def test_rope_write_keeps_the_unrotated_key_as_value(ops, dtype, nh, nkv, d, rd):
     from paged_llm_b200.parts.rope import RotaryEncoding
     ops.set_compute_dtype(dtype)
@@ -214,7 +214,7 @@ def test_rope_write_keeps_the_unrotated_key_as_value(ops, dtype, nh, nkv, d, rd)
 
 
 @pytest.mark.parametrize("M", [1, 7, 16])
-@pytest.mark.parametrize("nh,nkv,d,K", [(8, 1, 96, 320), (4, 2, 16, 64), (2, 2, 64, 128)])
+@pytest.mark.parametrize("nh,nkv,d,K", [(6, 2, 96, 256), (4, 2, 16, 64), (2, 2, 64, 128)])
 def test_fused_projection_with_rotation_and_values_from_keys(ops, M, nh, nkv, d, K):
     """Few tokens: projection, rotation and cache write are one kernel; against the separate kernels."""
     from paged_llm_b200.parts.rope import RotaryEncoding
@@ -271,7 +271,7 @@ def test_gelu_gate(ops, dtype, rows, I):
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
-@pytest.mark.parametrize("I,K", [(256, 320), (100, 96), (7, 32)])
+@pytest.mark.parametrize("I,K", [(224, 288), (100, 96), (7, 32)])
 def test_few_token_product_with_the_gelu_gate(ops, M, I, K):
     ops.set_compute_dtype(torch.bfloat16)
     h = randn(M, K, seed=1, dtype=torch.bfloat16)
@@ -295,7 +295,7 @@ def test_sums_into_the_stream(ops, dtype):
 # ---------------------------------------------------------------- routed experts
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,D,E,k,F,shared", [(5, 64, 6, 2, 32, 48), (300, 128, 4, 2, 64, 32), (40, 96, 5, 5, 20, None),
-                                              (1, 320, 12, 3, 64, 96), (16, 64, 8, 1, 16, None), (130, 72, 3, 2, 24, 8),
+                                              (1, 352, 10, 3, 48, 80), (16, 64, 8, 1, 16, None), (130, 72, 3, 2, 24, 8),
                                               (70, 64, 40, 4, 16, None)])
 def test_routed_experts(ops, dtype, T, D, E, k, F, shared):
     """Router, top-k, softmax over the chosen logits, experts and the shared expert behind its gate, in every

@@ -108,8 +108,8 @@ def test_first_visible_key():
 
 
 def test_plan_splits_only_the_keys_of_the_chunk():
-    # a decoded token at position 1,000 with chunks of 96: 41 keys, one split, whatever the context
-    plan = plan_attention([1], [1001], 4, 2, None, chunk=96, small_rows=16, large_rows=64, min_split_keys=64, num_sms=148)
+    # a decoded token at position 1,000 with chunks of 80: 41 keys, one split, whatever the context
+    plan = plan_attention([1], [1001], 4, 2, None, chunk=80, small_rows=16, large_rows=64, min_split_keys=64, num_sms=148)
     assert plan["small"].reshape(-1, 4).tolist() == [[0, 0, 0, 1]]
     plan = plan_attention([1], [1001], 4, 2, None, small_rows=16, large_rows=64, min_split_keys=64, num_sms=148)
     assert plan["small"].reshape(-1, 4)[0, 3] > 1
