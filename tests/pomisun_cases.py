@@ -76,6 +76,47 @@ CASES = {"P": (CASE_P, dict(seed=11, std=0.08, norm_std=0.1)),
          "R": (CASE_R, dict(seed=13, std=0.06, norm_std=0.05))}
 
 
+def generated_case(seed: int) -> tuple[dict, dict]:
+    """A configuration drawn from a seed: widths, head counts and sizes, rotated dimensions, chunks, caps, kinds of
+    feed-forward, the order of layers and the looped span all vary, within what the design allows."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([64, 96, 160, 200, 288, 384])
+    n_layers = rng.randint(2, 4)
+    layers = []
+    for _ in range(n_layers):
+        dim = rng.choice([16, 32, 48, 64, 80, 96, 128])
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 4, 5])
+        rot = None
+        if rng.random() < 0.85:
+            rot = {"dims": rng.choice([dim, dim, dim // 2, dim - 8 if dim > 16 else dim]), "base": rng.choice([100.0, 10000.0, 500000.0])}
+            if rng.random() < 0.7:
+                rot["scaling"] = {"factor": rng.choice([1.5, 2.0, 4.0, 8.0]), "original": rng.choice([32, 64, 256]),
+                                  "fast": rng.choice([8.0, 16.0, 32.0]), "slow": rng.choice([1.0, 2.0])}
+        mixer = _attn(heads, kv, dim, scale=rng.choice([1.0, 0.7, 1.3]) * dim ** -0.5,
+                      softcap=rng.choice([None, 5.0, 20.0, 50.0]), chunk=rng.choice([None, 7, 16, 33, 64, 100]), rot=rot)
+        kind = rng.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": rng.choice([24, 64, 100, 256])}
+        elif kind == "moe":
+            experts = rng.choice([2, 3, 8, 12, 20])
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([8, 20, 32, 64])},
+                   "router": {"experts": experts, "top": rng.randint(1, min(experts, 4))}}
+            if rng.random() < 0.6:
+                mlp["shared"] = {"ff": rng.choice([16, 40, 96])}
+        else:
+            mlp = None
+        layers.append(_layer(mixer, mlp))
+    cfg = {"architecture": "Pomisun", "vocab": rng.choice([50, 131, 300, 777]), "width": width,
+           "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randint(0, n_layers - 1)
+        stop = rng.randint(start + 1, n_layers)
+        cfg["loop"] = {"start": start, "stop": stop, "times": rng.randint(1, 3)}
+    return cfg, dict(seed=seed, std=rng.choice([0.05, 0.1]), norm_std=0.1)
+
+
 def make_folder(path, hf_cfg: dict, init: dict, dtype: str = "float32") -> str:
     return write_model_folder(str(path), PomisunConfig.from_hf_dict(hf_cfg), dtype=dtype, **init)
 
@@ -106,24 +147,28 @@ def plain_logits(folder: str, tokens) -> np.ndarray:
 def clear_requests(folder: str, vocab: int, lengths, seed: int = 0, margin: float = 0.02) -> dict[str, list[int]]:
     """Random requests on which no router of the model comes close to a tie (the last chosen expert leads the
     first rejected one by `margin` of the logits' spread at every token): the bfloat16 engine then chooses the
-    experts the plain model chooses, and the two differ by rounding only."""
+    experts the plain model chooses, and the two differ by rounding only.  A length for which 100 draws find no
+    such request is shortened."""
     cfg, w = read_folder(folder)
     out = {}
     for i, n in enumerate(lengths):
-        for attempt in range(400):
-            g = torch.Generator().manual_seed(seed * 100003 + i * 401 + attempt)
-            toks = torch.randint(0, vocab, (n,), generator=g).tolist()
-            plain_pomisun.ROUTER_MARGINS = []
-            try:
-                plain_pomisun.forward(cfg, w, toks)
-                worst = min(plain_pomisun.ROUTER_MARGINS, default=1.0)
-            finally:
-                plain_pomisun.ROUTER_MARGINS = None
-            if worst >= margin:
-                out[f"r{i}"] = toks
-                break
-        else:
-            raise AssertionError(f"no request of {n} tokens without a close call in 400 draws")
+        while f"r{i}" not in out:
+            for attempt in range(100):
+                g = torch.Generator().manual_seed(seed * 100003 + i * 401 + attempt)
+                toks = torch.randint(0, vocab, (n,), generator=g).tolist()
+                plain_pomisun.ROUTER_MARGINS = []
+                try:
+                    plain_pomisun.forward(cfg, w, toks)
+                    worst = min(plain_pomisun.ROUTER_MARGINS, default=1.0)
+                finally:
+                    plain_pomisun.ROUTER_MARGINS = None
+                if worst >= margin:
+                    out[f"r{i}"] = toks
+                    break
+            else:
+                if n <= 2:
+                    raise AssertionError("no request without a close call, however short")
+                n = max(2, n * 2 // 3)           # (few experts and many routed layers: a shorter request)
     return out
 
 

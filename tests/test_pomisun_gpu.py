@@ -15,7 +15,7 @@ import torch
 
 from tests import plain_pomisun, schedules
 from tests.helpers import assert_bf16_close_to_f32, assert_logits_close, requests_for
-from tests.pomisun_cases import CASES, case_folder, clear_requests, plain_greedy, plain_logits
+from tests.pomisun_cases import CASES, case_folder, clear_requests, generated_case, make_folder, plain_greedy, plain_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -470,6 +470,22 @@ def test_graph_and_eager_decode_agree(folders, requests, dtype):
     assert rp_a.runner.num_graph_steps > 0 and rp_b.runner.num_graph_steps == 0
     for k in a:
         assert_logits_close(a[k], b[k], dtype, f"graph vs eager step {k}")
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_generated_configurations(tmp_path, seed):
+    """Other sizes, head counts, layer orders, chunks and constants than the fixed cases: a mixed schedule of four
+    requests with reused pages, float32 against the plain model at every position, then bfloat16."""
+    hf, init = generated_case(seed)
+    folder = make_folder(tmp_path, hf, init, dtype="bfloat16")
+    # (bfloat16 on shorter requests, drawn so that no router comes close to a tie)
+    for dtype, reqs in (("float32", requests_for(hf["vocab"], (37, 3, 110, 64, 18, 75), seed=seed)),
+                        ("bfloat16", clear_requests(folder, hf["vocab"], (30, 3, 48, 17, 40), seed=seed, margin=0.08))):
+        steps, max_tokens = schedules.mixed(reqs, live=4, seed=seed)
+        outputs, _ = replay(folder, dtype, steps, max_tokens)
+        got = schedules.collect(steps, outputs)
+        for rid, toks in reqs.items():
+            assert_logits_close(got[rid], plain_logits(folder, toks), dtype, f"generated {seed}/{dtype}/{rid}")
 
 
 def test_long_decoding_over_many_chunks(folders):

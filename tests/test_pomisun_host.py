@@ -18,7 +18,7 @@ from paged_llm_b200.models import build_model, pomisun_spec
 from paged_llm_b200.parts.rope import RotaryEncoding
 from tests import plain_pomisun, schedules
 from tests.helpers import assert_logits_close, requests_for
-from tests.pomisun_cases import CASE_P, CASE_Q, CASES, case_folder, plain_greedy, plain_logits
+from tests.pomisun_cases import CASE_P, CASE_Q, CASES, case_folder, generated_case, make_folder, plain_greedy, plain_logits
 from tests.torch_ops import TorchOps
 
 LENGTHS = {"P": (5, 30, 77, 49, 24, 2, 60, 71, 35, 50), "Q": (1, 41, 90, 13, 80, 55, 66, 47), "R": (3, 70, 33, 65, 90, 41, 58, 77)}
@@ -164,6 +164,19 @@ def test_replay_schedules_on_the_host(folders, name, schedule):
         assert_logits_close(got[rid], plain_logits(folders[name], toks), "float32", f"{schedule}/{name}/{rid}")
     if schedule == "mixed":
         assert sum(-(-len(t) // 8) for t in reqs.values()) > rp.cm.num_blocks, "pages must be used again"
+
+
+@pytest.mark.parametrize("seed", range(10, 14))
+def test_generated_configurations_on_the_host(tmp_path, seed):
+    hf, init = generated_case(seed)
+    assert PomisunConfig.from_hf_dict(PomisunConfig.from_hf_dict(hf).to_hf_dict()) == PomisunConfig.from_hf_dict(hf)
+    folder = make_folder(tmp_path, hf, init)
+    reqs = requests_for(hf["vocab"], (21, 2, 70, 45), seed=seed)
+    steps, max_tokens = schedules.mixed(reqs, live=3, seed=seed)
+    outputs, _ = replay(folder, steps, max_tokens)
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert_logits_close(got[rid], plain_logits(folder, toks), "float32", f"generated {seed}/{rid}")
 
 
 def test_greedy_generation_on_the_host(folders):
