@@ -70,7 +70,9 @@ __device__ __forceinline__ void tc_drain_row(const TcParams& p, uint32_t acc, in
                         for (int e = 0; e < 2; ++e) {
                             const float gate = __bfloat162float(__float2bfloat16_rn(g[q * 8 + 2 * i + e]));
                             const float up = __bfloat162float(__float2bfloat16_rn(u[q * 8 + 2 * i + e]));
-                            o[e] = (p.act == 1 ? gelu_tanh_f(gate) : gate / (1.0f + __expf(-gate))) * up;
+                            // (the fast division: the IEEE one leaves its fast path for a numerator of zero, and the rows
+                            // that pad a tile of the grouped form are all zeros: 175 against 96 us for one such product)
+                            o[e] = (p.act == 1 ? gelu_tanh_f(gate) : __fdividef(gate, 1.0f + __expf(-gate))) * up;
                         }
                         w[i] = pack_bf16x2(o[0], o[1]);
                     }

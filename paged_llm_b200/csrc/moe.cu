@@ -313,19 +313,46 @@ __global__ void __launch_bounds__(256) moe_gemm_plain_kernel(MoeGemm p) {
 }
 
 // y[t] = sum_j w_j * pair_out[row_j]  (+ gate[t] * shared[t]), float32, with row_j = place[t * k + j] (null:
-// t * k + j) and w_j = weight[t * k + j] (null: 1, the rows are weighted already).
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, int k, const int* __restrict__ place,
+// t * k + j) and w_j = weight[t * k + j] (null: 1, the rows are weighted already).  pair_out is float32 or (from
+// the grouped tensor-core product) bfloat16.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+template <typename TP, typename T>
+__global__ void moe_combine_kernel(const TP* __restrict__ pair_out, int k, const int* __restrict__ place,
                                    const float* __restrict__ weight, const T* __restrict__ shared,
-                                   const float* __restrict__ gate, float* __restrict__ y, int D) {
+                                   const float* __restrict__ gate, float* __restrict__ y, int D, int vec) {
     const size_t t = blockIdx.x;
     const float gt = shared != nullptr ? gate[t] : 0.f;
+    if (vec) {
+        // four columns per thread (D % 4 == 0, 16-byte aligned bases)
+        for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < k; ++j) {
+                const long long row = place != nullptr ? place[t * k + j] : (long long)(t * k + j);
+                if (row < 0) continue;
+                const float4 v = load4(pair_out + (size_t)row * D + c);
+                const float w = weight != nullptr ? weight[t * k + j] : 1.f;
+                s.x = fmaf(w, v.x, s.x); s.y = fmaf(w, v.y, s.y); s.z = fmaf(w, v.z, s.z); s.w = fmaf(w, v.w, s.w);
+            }
+            if (shared != nullptr) {
+                const float4 v = load4(shared + t * D + c);
+                s.x = fmaf(gt, v.x, s.x); s.y = fmaf(gt, v.y, s.y); s.z = fmaf(gt, v.z, s.z); s.w = fmaf(gt, v.w, s.w);
+            }
+            *reinterpret_cast<float4*>(y + t * D + c) = s;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float s = 0.f;
         for (int j = 0; j < k; ++j) {
             const long long row = place != nullptr ? place[t * k + j] : (long long)(t * k + j);
             if (row < 0) continue;
-            const float v = pair_out[(size_t)row * D + c];
+            const float v = to_float(pair_out[(size_t)row * D + c]);
             s = weight != nullptr ? fmaf(weight[t * k + j], v, s) : s + v;
         }
         if (shared != nullptr) s = fmaf(gt, to_float(shared[t * D + c]), s);
@@ -425,18 +452,24 @@ PL_EXPORT int pl_moe_gemm(const void* A, int lda, int a_div, const void* W, void
     return 0;
 }
 
-PL_EXPORT int pl_moe_combine(const float* pair_out, int k, const int* place, const float* weight, const void* shared,
-                             int shared_dtype, const float* gate, float* y, int tokens, int D, cudaStream_t stream) {
+PL_EXPORT int pl_moe_combine(const void* pair_out, int pair_dtype, int k, const int* place, const float* weight,
+                             const void* shared, int shared_dtype, const float* gate, float* y, int tokens, int D,
+                             cudaStream_t stream) {
     if (tokens == 0) return 0;
     PL_REQUIRE(tokens > 0 && D > 0 && k > 0, "moe_combine: bad sizes");
     const int threads = D >= 1024 ? 256 : 128;
-    if (shared == nullptr || shared_dtype == PL_F32)
-        moe_combine_kernel<float><<<tokens, threads, 0, stream>>>(pair_out, k, place, weight, (const float*)shared, gate, y, D);
-    else if (shared_dtype == PL_BF16)
-        moe_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(pair_out, k, place, weight,
-                                                                          (const __nv_bfloat16*)shared, gate, y, D);
-    else
-        return pl_fail("moe_combine: unknown dtype %d", shared_dtype);
+    const bool sf = shared == nullptr || shared_dtype == PL_F32;
+    const int vec = D % 4 == 0 && (((uintptr_t)pair_out | (uintptr_t)shared | (uintptr_t)y) & 15) == 0;
+    PL_REQUIRE(sf || shared_dtype == PL_BF16, "moe_combine: unknown dtype %d", shared_dtype);
+    if (pair_dtype == PL_F32) {
+        if (sf) moe_combine_kernel<float, float><<<tokens, threads, 0, stream>>>((const float*)pair_out, k, place, weight, (const float*)shared, gate, y, D, vec);
+        else moe_combine_kernel<float, __nv_bfloat16><<<tokens, threads, 0, stream>>>((const float*)pair_out, k, place, weight, (const __nv_bfloat16*)shared, gate, y, D, vec);
+    } else if (pair_dtype == PL_BF16) {
+        if (sf) moe_combine_kernel<__nv_bfloat16, float><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)pair_out, k, place, weight, (const float*)shared, gate, y, D, vec);
+        else moe_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)pair_out, k, place, weight, (const __nv_bfloat16*)shared, gate, y, D, vec);
+    } else {
+        return pl_fail("moe_combine: unknown dtype %d", pair_dtype);
+    }
     PL_LAUNCHED("moe_combine");
     return 0;
 }

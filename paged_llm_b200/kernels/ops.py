@@ -467,9 +467,10 @@ class CudaOps:
             inter = torch.empty((cap, F), dtype=h.dtype, device=dev)
             _check(self.core, self.core.pl_gemm_tc_grouped(self._p(xs), D, self._p(w_gate_up), self._p(inter), F, cap, F, D,
                                                            2, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
-            pair_out = torch.empty((cap, D), dtype=torch.float32, device=dev)
+            # (each expert's output is rounded to bfloat16, as a dense layer's branch is; the weighted sum is float32)
+            pair_out = torch.empty((cap, D), dtype=torch.bfloat16, device=dev)
             _check(self.core, self.core.pl_gemm_tc_grouped(self._p(inter), F, self._p(w_down), self._p(pair_out), D, cap, D, F,
-                                                           1, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
+                                                           0, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
             self.launches += 5
         else:
             inter = torch.empty((pairs, F), dtype=h.dtype, device=dev)
@@ -485,7 +486,8 @@ class CudaOps:
         if shared is not None:
             s = self.linear(self.gated_act_linear(h, shared[0], shared_activation), shared[1])
         y = torch.empty((T, D), dtype=torch.float32, device=dev)
-        _check(lib, lib.pl_moe_combine(self._p(pair_out), top_k, self._p(place), self._p(top_w) if grouped_tc else c_void_p(0),
+        _check(lib, lib.pl_moe_combine(self._p(pair_out), self._code(pair_out), top_k, self._p(place),
+                                       self._p(top_w) if grouped_tc else c_void_p(0),
                                        self._p(s), self._code(s) if s is not None else PL_F32,
                                        self._p(gate), self._p(y), T, D, self._stream))
         self.launches += 1
