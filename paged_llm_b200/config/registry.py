@@ -58,6 +58,10 @@ def _register_builtin() -> None:
     from .pomisun import PomisunConfig
     if "Pomisun" not in ARCHITECTURES:
         register_architecture("Pomisun", PomisunConfig, pomisun_spec)
+    from ..models.rokarax import rokarax_spec
+    from .rokarax import RokaraxConfig
+    if "Rokarax" not in ARCHITECTURES:
+        register_architecture("Rokarax", RokaraxConfig, rokarax_spec)
 
 
 _register_builtin()

@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const int g = lane >> 2, t4 = lane & 3;
     int pos[2], first[2];
     float slope[2];
+    const float* brow[2];
     constexpr bool modified = MOD;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -196,6 +197,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         pos[h] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
         first[h] = attn_first_key(p, max(pos[h], 0));
         slope[h] = MOD && p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
+        brow[h] = MOD && p.dist_bias != nullptr && R < it.rows_total ? p.dist_bias + (size_t)(kvh * G + R % G) * p.dist_len : nullptr;
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float oacc[DPAD / 8][4];
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                         const int pr = pos[e >> 1];
                         const bool vis = n < hi_cur && n <= pr && n >= first[e >> 1];
                         const float s = !vis ? -INFINITY
-                                        : modified ? attn_score(p, sacc[j][e], slope[e >> 1], n, pr) * LOG2E
+                                        : modified ? attn_score(p, sacc[j][e], slope[e >> 1], n, pr, brow[e >> 1]) * LOG2E
                                                    : sacc[j][e] * scale_log2;
                         sacc[j][e] = s;
                         mx[e >> 1] = fmaxf(mx[e >> 1], s);
@@ -671,11 +673,12 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     // prompt portions of head sizes 64 and 128 with a cap on the scores (and no bias by distance): the
     // tcgen05 kernel applies the cap itself
     static const bool no_tc_cap = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
-    if (p.softcap > 0.f && p.slopes == nullptr && p.rope_table == nullptr && p.cluster <= 0 && !p.is_small &&
+    if (p.softcap > 0.f && p.slopes == nullptr && p.dist_bias == nullptr && p.rope_table == nullptr && p.cluster <= 0 && !p.is_small &&
         p.d == PL_DPAD && !no_tc_cap && tc2::takes(p))
         return tc2::launch<PL_DPAD>(p, stream);
 #endif
-    if (p.softcap > 0.f || p.slopes != nullptr) {
+    PL_REQUIRE(p.dist_bias == nullptr || p.dist_len > 0, "attention_bf16: a bias by distance of %d entries", p.dist_len);
+    if (p.softcap > 0.f || p.slopes != nullptr || p.dist_bias != nullptr) {
         PL_REQUIRE(p.rope_table == nullptr, "attention_bf16: score modifiers and rotary positions inside the kernel "
                                             "do not combine");
         // the score modifiers live in instantiations of their own of the mma.sync kernel (the tcgen05

@@ -32,12 +32,14 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
     }
     int pos[4], first[4];
     float m[4], l[4], acc[4][F32_MAXD / 32], slope[4];
+    const float* brow[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
         const int R = it.row_base + warp * 4 + rr;
         pos[rr] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
         first[rr] = attn_first_key(p, max(pos[rr], 0));
         slope[rr] = p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
+        brow[rr] = p.dist_bias != nullptr && R < it.rows_total ? p.dist_bias + (size_t)(kvh * G + R % G) * p.dist_len : nullptr;
         m[rr] = -INFINITY;
         l[rr] = 0.f;
 #pragma unroll
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
             const float* kr = Ks + lane * (d + 1);
             float s = 0.f;
             for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
-            s = attn_score(p, s, slope[rr], n, pos[rr]);
+            s = attn_score(p, s, slope[rr], n, pos[rr], brow[rr]);
             const bool vis = n < it.key_hi && n <= pos[rr] && n >= first[rr];
             const float m_new = fmaxf(m[rr], warp_max(vis ? s : -INFINITY));
             if (m_new == -INFINITY) continue;
@@ -162,6 +164,7 @@ int pl_attn_check(const AttnParams& p, const char* who) {
     PL_REQUIRE(p.chunk >= 0, "%s: chunk=%d", who, p.chunk);
     PL_REQUIRE(p.max_splits >= 1, "%s: max_splits=%d", who, p.max_splits);
     PL_REQUIRE(p.softcap >= 0.f, "%s: softcap=%f must not be negative", who, (double)p.softcap);
+    PL_REQUIRE(p.dist_bias == nullptr || p.dist_len > 0, "%s: a bias by distance of %d entries", who, p.dist_len);
     return 0;
 }
 

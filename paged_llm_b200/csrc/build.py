@@ -34,13 +34,15 @@ NVCC_FLAGS += os.environ.get("PAGED_LLM_B200_NVCC_FLAGS", "").split()
 HEAD_DIM_BUILDS = (16, 32, 64, 128, 256)
 
 MODULES: dict[str, list[str]] = {
-    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_f32.cu",
+    "core": ["common.cu", "elementwise.cu", "mixers.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_f32.cu",
              "sampling.cu"],
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
     # decode attention whose scratch is a static array of the library (see attention_decode_static.h)
     "attn_static": ["common.cu", "attention_decode_static.cu"],
     # routed experts (router, pairs sorted by expert, grouped products, weighted sum)
     "moe": ["common.cu", "moe.cu"],
+    # state-space mixer (short convolution, recurrence, gated norm in parts)
+    "ssm": ["common.cu", "ssm.cu"],
 }
 
 

@@ -141,6 +141,12 @@ struct AttnParams {
     // Chunked mask: > 0: positions are cut into chunks of this many, counted from position 0 of the request, and a
     // query sees only the keys of its own chunk (at or before itself).  0: none.  Combines with `window`.
     int chunk;
+    // Learned bias by distance: [nh, dist_len] float32 or null.  Head h adds dist_bias[h][min(query position -
+    // key position, dist_len - 1)] to its score (after the cap, beside the slopes): whatever function of the
+    // distance the model defines (buckets, a table per head) is laid out by distance on the host, and all
+    // distances from dist_len - 1 on share the last entry.
+    const float* dist_bias;
+    int dist_len;
 };
 
 // The lowest key position that the query at `pos` may see (the highest is `pos` itself).
@@ -152,8 +158,12 @@ __device__ __forceinline__ int attn_first_key(const AttnParams& p, int pos) {
 }
 
 // The score of one (query row, key) pair from the raw dot product, in natural-log units.
-__device__ __forceinline__ float attn_score(const AttnParams& p, float dot, float slope, int key_pos, int query_pos) {
+// `bias_row`: the row of AttnParams::dist_bias of this query's head, or null.
+__device__ __forceinline__ float attn_score(const AttnParams& p, float dot, float slope, int key_pos, int query_pos,
+                                            const float* bias_row = nullptr) {
     float s = dot * p.scale;
     if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
-    return s + slope * (float)(key_pos - query_pos);
+    s += slope * (float)(key_pos - query_pos);
+    if (bias_row != nullptr) s += __ldg(bias_row + min(max(query_pos - key_pos, 0), p.dist_len - 1));
+    return s;
 }

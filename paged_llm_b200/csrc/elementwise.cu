@@ -12,7 +12,7 @@
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                 int H, int V) {
+                                 int H, int V, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -34,23 +34,25 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
                     v = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
                 }
             }
+            if (scale != 1.0f) v = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
             *reinterpret_cast<float4*>(o + c) = v;
         }
         return;
     }
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = valid ? to_float(row[c]) : 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = valid ? to_float(row[c]) * scale : 0.f;
 }
 
+// `scale` multiplies every element (1: the table's rows as they are), in float32.
 PL_EXPORT int pl_embedding(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V,
-                           cudaStream_t stream) {
+                           float scale, cudaStream_t stream) {
     if (T == 0) return 0;
     PL_REQUIRE(T > 0 && H > 0 && V > 0, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == PL_F32)
-        PL_CUDA(launch_pdl(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V));
+        PL_CUDA(launch_pdl(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, scale));
     else if (table_dtype == PL_BF16)
         PL_CUDA(launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
-                           (const __nv_bfloat16*)table, ids, out, H, V));
+                           (const __nv_bfloat16*)table, ids, out, H, V, scale));
     else
         return pl_fail("embedding: unknown dtype %d", table_dtype);
     return 0;

@@ -1,0 +1,334 @@
+// Kernels around the attention kernels for mixers that are not plain grouped-query attention, and the
+// dynamic-tanh norm.
+//
+//  * dynamic tanh: y = tanh(alpha x) w + b, elementwise, with the residual sum fused in front of it
+//    and a second dynamic tanh (the norm behind a branch) fused in front of the sum;
+//  * a norm over the whole query projection and the whole key projection (all heads at once), the
+//    queries laid out for the attention kernel and keys and values written to their page slots, with
+//    head sizes padded to the size the cache was made for (keys and values of different sizes);
+//  * a sigmoid gate on the heads' outputs;
+//  * latent attention: the normed latents, the shared rotated key part and the latent written to the
+//    cache as one key/value head; the queries assembled as [absorbed query | rotated part].
+//
+// Norms, angles, gates and sums are float32 whatever the activations' type is.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ dynamic tanh
+struct DytParams {
+    const float* alpha;     // one scalar on the device
+    const float* w;         // [H]
+    const float* b;         // [H]
+};
+
+// x (float32 stream, may be null) += post(branch); y = pre(x).  Either norm may be absent (alpha null):
+// without `post` the branch is added as it is, without `pre` nothing is written to y.  With x null,
+// y = pre(branch) (a norm alone, of a tensor that is not the stream).
+template <typename TB, typename TY>
+__global__ void dyt_kernel(float* __restrict__ x, const TB* __restrict__ branch, DytParams post, DytParams pre,
+                           TY* __restrict__ y, long long n, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float a_post = post.alpha != nullptr ? __ldg(post.alpha) : 0.f;
+    const float a_pre = pre.alpha != nullptr ? __ldg(pre.alpha) : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % H);
+        float v = 0.f;
+        if (branch != nullptr) {
+            v = to_float(branch[i]);
+            if (post.alpha != nullptr) v = tanhf(a_post * v) * __ldg(post.w + c) + __ldg(post.b + c);
+        }
+        if (x != nullptr) {
+            v += x[i];
+            if (branch != nullptr) x[i] = v;
+        }
+        if (y != nullptr) y[i] = from_float<TY>(tanhf(a_pre * v) * __ldg(pre.w + c) + __ldg(pre.b + c));
+    }
+}
+
+template <typename TB, typename TY>
+static int launch_dyt(float* x, const void* branch, DytParams post, DytParams pre, void* y, long long n, int H,
+                      cudaStream_t stream) {
+    const long long blocks = (n + 255) / 256;
+    PL_CUDA(launch_pdl(dyt_kernel<TB, TY>, dim3((unsigned)(blocks < 4096 ? blocks : 4096)), dim3(256), 0, stream, x,
+                       (const TB*)branch, post, pre, (TY*)y, n, H));
+    return 0;
+}
+
+PL_EXPORT int pl_dyt(float* x, const void* branch, int branch_dtype, const float* post_alpha, const float* post_w,
+                     const float* post_b, const float* pre_alpha, const float* pre_w, const float* pre_b, void* y,
+                     int y_dtype, long long rows, int H, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    PL_REQUIRE(rows > 0 && H > 0, "dyt: bad sizes rows=%lld H=%d", rows, H);
+    PL_REQUIRE(x != nullptr || branch != nullptr, "dyt: nothing to normalise");
+    PL_REQUIRE(y == nullptr || pre_alpha != nullptr, "dyt: an output without a norm");
+    DytParams post{post_alpha, post_w, post_b}, pre{pre_alpha, pre_w, pre_b};
+    const long long n = rows * H;
+    if (y == nullptr) pre.alpha = nullptr;
+    const bool bf_b = branch != nullptr && branch_dtype == PL_BF16;
+    const bool bf_y = y != nullptr && y_dtype == PL_BF16;
+    if (bf_b && bf_y) return launch_dyt<__nv_bfloat16, __nv_bfloat16>(x, branch, post, pre, y, n, H, stream);
+    if (bf_b) return launch_dyt<__nv_bfloat16, float>(x, branch, post, pre, y, n, H, stream);
+    if (bf_y) return launch_dyt<float, __nv_bfloat16>(x, branch, post, pre, y, n, H, stream);
+    return launch_dyt<float, float>(x, branch, post, pre, y, n, H, stream);
+}
+
+// ------------------------------------------------------------------ page slot of a token
+struct SlotArgs {
+    const int* positions;
+    const int* token_seq;
+    const int* block_table;
+    int bt_stride, num_pages, ps;
+};
+
+// Offset (in elements of a [pages, 2, nkv, ps, D] pool) of the key row of kv head 0 of token t, or -1.
+__device__ __forceinline__ long long key_slot(const SlotArgs& a, int t, int s, int pos, int nkv, int D) {
+    if (s < 0 || pos < 0) return -1;
+    const int page = a.block_table[(size_t)s * a.bt_stride + pos / a.ps];
+    if (page < 0 || page >= a.num_pages) return -1;
+    return (((long long)page * 2) * nkv * a.ps + pos % a.ps) * D;
+}
+
+// ------------------------------------------------------------------ norm over whole projections + cache write
+// proj row: [q: nh*d | k: nkv*d | v: nkv*dv | ...] (k and v only with has_kv).  One block per token.
+//   q' = q / sqrt(mean(q^2) + eps) * qw over all nh*d elements at once, the same for k with kw.
+// Q out: [T, nh*D], head h at h*D, columns d..D zero.  K and V go to the page slot, padded to D with zeros.
+template <typename T>
+__global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ qw,
+                                  const float* __restrict__ kw, float eps, T* __restrict__ q_out, T* __restrict__ kv,
+                                  SlotArgs sa, int nh, int nkv, int d, int dv, int D, int has_kv, int write) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int s = sa.token_seq[t];
+    T* qo = q_out + (size_t)t * nh * D;
+    if (s < 0) {                                   // a row that pads the step
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) qo[i] = from_float<T>(0.f);
+        return;
+    }
+    const T* row = proj + (size_t)t * ld;
+    const int nq = nh * d, nk = nkv * d;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float v = to_float(row[i]);
+        sq += v * v;
+    }
+    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int h = i / D, c = i - h * D;
+        qo[i] = from_float<T>(c < d ? to_float(row[h * d + c]) * rq * __ldg(qw + h * d + c) : 0.f);
+    }
+    if (!has_kv || !write) return;
+    const long long slot = key_slot(sa, t, s, sa.positions[t], nkv, D);
+    float sk = 0.f;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const float v = to_float(row[nq + i]);
+        sk += v * v;
+    }
+    const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+    if (slot < 0) return;
+    const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
+    for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
+        const int h = i / D, c = i - h * D;
+        const float kk = c < d ? to_float(row[nq + h * d + c]) * rk * __ldg(kw + h * d + c) : 0.f;
+        const float vv = c < dv ? to_float(row[nq + nk + h * dv + c]) : 0.f;
+        kv[slot + h * head_stride + c] = from_float<T>(kk);
+        kv[slot + v_off + h * head_stride + c] = from_float<T>(vv);
+    }
+}
+
+PL_EXPORT int pl_normed_qkv_write(const void* proj, int dtype, int T, int ld, const float* qw, const float* kw, float eps,
+                                  void* q_out, void* kv, const int* positions, const int* token_seq,
+                                  const int* block_table, int bt_stride, int num_pages, int ps, int nh, int nkv, int d,
+                                  int dv, int D, int has_kv, int write, cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(nh > 0 && nkv > 0 && d > 0 && dv > 0 && D >= d && D >= dv, "normed_qkv_write: bad head sizes d=%d dv=%d D=%d", d,
+               dv, D);
+    SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
+    if (dtype == PL_F32)
+        normed_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, qw, kw, eps, (float*)q_out, (float*)kv, sa,
+                                                        nh, nkv, d, dv, D, has_kv, write);
+    else if (dtype == PL_BF16)
+        normed_qkv_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, qw, kw, eps,
+                                                                (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv, sa, nh, nkv,
+                                                                d, dv, D, has_kv, write);
+    else
+        return pl_fail("normed_qkv_write: unknown dtype %d", dtype);
+    PL_LAUNCHED("normed_qkv_write");
+    return 0;
+}
+
+// ------------------------------------------------------------------ sigmoid gate on the heads' outputs
+// out[t, h*dv + c] = o[t, h*D + c] * sigmoid(gate[t, h*dv + c]),  c < dv (the padding of a head is dropped).
+// gate null: the copy without the padding.
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ o, int D, const T* __restrict__ gate, int ldg, T* __restrict__ out,
+                                 long long n, int nh, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = nh * dv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / row;
+        const int e = (int)(i - t * row), h = e / dv, c = e - h * dv;
+        float v = to_float(o[(size_t)t * nh * D + h * D + c]);
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * ldg + e])));
+        out[i] = from_float<T>(v);
+    }
+}
+
+PL_EXPORT int pl_head_gate(const void* o, int dtype, int T, int D, const void* gate, int ldg, void* out, int nh, int dv,
+                           cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(nh > 0 && dv > 0 && D >= dv, "head_gate: bad sizes dv=%d D=%d", dv, D);
+    const long long n = (long long)T * nh * dv;
+    const long long blocks = (n + 255) / 256;
+    const dim3 grid((unsigned)(blocks < 4096 ? blocks : 4096));
+    if (dtype == PL_F32)
+        PL_CUDA(launch_pdl(head_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)o, D, (const float*)gate, ldg,
+                           (float*)out, n, nh, dv));
+    else if (dtype == PL_BF16)
+        PL_CUDA(launch_pdl(head_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o, D,
+                           (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, n, nh, dv));
+    else
+        return pl_fail("head_gate: unknown dtype %d", dtype);
+    return 0;
+}
+
+// ------------------------------------------------------------------ latent attention
+// Rotation of pairs (2i, 2i+1), i < half, with (cos, sin) of `table` [positions, half]; the rest passes.
+__device__ __forceinline__ float rot_elem(const float2* cs, int half, bool rotate, float self, float partner, int c) {
+    if (!rotate || c >= 2 * half) return self;
+    const float2 t = cs[c >> 1];
+    return (c & 1) ? self * t.x + partner * t.y : self * t.x - partner * t.y;
+}
+
+// down row: [cq: q_rank | c: kv_rank | kr: rot_dim].  One block per token:
+//   cq_out = cq / rms(cq) * qw;  c' = c / rms(c) * cw;  kr' = rotate(kr, position)
+//   key slot  [c' | kr' | 0 ..D),  value slot [c' | 0 ..D)   (one kv head)
+template <typename T>
+__global__ void latent_kv_kernel(const T* __restrict__ down, int ld, const float* __restrict__ qw,
+                                 const float* __restrict__ cw, float eps, T* __restrict__ cq_out, T* __restrict__ kv,
+                                 SlotArgs sa, const float2* __restrict__ table, int table_len, int half, int q_rank,
+                                 int kv_rank, int rot_dim, int D, int write) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int s = sa.token_seq[t];
+    T* cq = cq_out + (size_t)t * q_rank;
+    if (s < 0) {
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(0.f);
+        return;
+    }
+    const T* row = down + (size_t)t * ld;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+        const float v = to_float(row[i]);
+        sq += v * v;
+    }
+    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(to_float(row[i]) * rq * __ldg(qw + i));
+    if (!write) return;
+    float sc = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
+        const float v = to_float(row[q_rank + i]);
+        sc += v * v;
+    }
+    const float rc = 1.0f / sqrtf(block_sum(sc, red) / (float)kv_rank + eps);
+    const int pos = sa.positions[t];
+    const long long slot = key_slot(sa, t, s, pos, 1, D);
+    if (slot < 0) return;
+    const bool rotate = half > 0 && pos < table_len;
+    const float2* cs = table + (size_t)pos * half;
+    const T* kr = row + q_rank + kv_rank;
+    const size_t v_off = (size_t)sa.ps * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float kk = 0.f, vv = 0.f;
+        if (i < kv_rank) {
+            kk = vv = to_float(from_float<T>(to_float(row[q_rank + i]) * rc * __ldg(cw + i)));
+        } else if (i < kv_rank + rot_dim) {
+            const int c = i - kv_rank;
+            const float partner = (c ^ 1) < rot_dim ? to_float(kr[c ^ 1]) : 0.f;
+            kk = rot_elem(cs, half, rotate, to_float(kr[c]), partner, c);
+        }
+        kv[slot + i] = from_float<T>(kk);
+        kv[slot + v_off + i] = from_float<T>(vv);
+    }
+}
+
+PL_EXPORT int pl_latent_kv_write(const void* down, int dtype, int T, int ld, const float* qw, const float* cw, float eps,
+                                 void* cq_out, void* kv, const int* positions, const int* token_seq,
+                                 const int* block_table, int bt_stride, int num_pages, int ps, const float* table,
+                                 int table_len, int rotary_dims, int q_rank, int kv_rank, int rot_dim, int D, int write,
+                                 cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && D >= kv_rank + rot_dim, "latent_kv_write: bad sizes");
+    PL_REQUIRE(rotary_dims % 2 == 0 && rotary_dims <= rot_dim, "latent_kv_write: %d rotated dimensions of %d", rotary_dims, rot_dim);
+    SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
+    const int half = table != nullptr ? rotary_dims / 2 : 0;
+    if (dtype == PL_F32)
+        latent_kv_kernel<float><<<T, 128, 0, stream>>>((const float*)down, ld, qw, cw, eps, (float*)cq_out, (float*)kv, sa,
+                                                       (const float2*)table, table_len, half, q_rank, kv_rank, rot_dim, D,
+                                                       write);
+    else if (dtype == PL_BF16)
+        latent_kv_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)down, ld, qw, cw, eps,
+                                                               (__nv_bfloat16*)cq_out, (__nv_bfloat16*)kv, sa,
+                                                               (const float2*)table, table_len, half, q_rank, kv_rank,
+                                                               rot_dim, D, write);
+    else
+        return pl_fail("latent_kv_write: unknown dtype %d", dtype);
+    PL_LAUNCHED("latent_kv_write");
+    return 0;
+}
+
+// Q out [T, nh*D]: head h = [q_abs[t, h, 0..kv_rank) | rotate(q[t, h, d..d+rot_dim)) | 0 ..D).
+// q_abs: [T, nh*kv_rank] (the unrotated part of the query multiplied into the key up-projection);
+// q: [T, nh*(d + rot_dim)].
+template <typename T>
+__global__ void latent_q_kernel(const T* __restrict__ q_abs, const T* __restrict__ q, T* __restrict__ q_out,
+                                const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                const float2* __restrict__ table, int table_len, int half, int nh, int d, int rot_dim,
+                                int kv_rank, int D) {
+    const int t = blockIdx.x;
+    const int s = token_seq[t];
+    T* qo = q_out + (size_t)t * nh * D;
+    if (s < 0) {
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) qo[i] = from_float<T>(0.f);
+        return;
+    }
+    const int pos = positions[t];
+    const bool rotate = half > 0 && pos >= 0 && pos < table_len;
+    const float2* cs = table + (size_t)max(pos, 0) * half;
+    const T* qa = q_abs + (size_t)t * nh * kv_rank;
+    const T* qr = q + (size_t)t * nh * (d + rot_dim);
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int h = i / D, c = i - h * D;
+        float v = 0.f;
+        if (c < kv_rank) {
+            v = to_float(qa[h * kv_rank + c]);
+        } else if (c < kv_rank + rot_dim) {
+            const int e = c - kv_rank;
+            const T* part = qr + h * (d + rot_dim) + d;
+            const float partner = (e ^ 1) < rot_dim ? to_float(part[e ^ 1]) : 0.f;
+            v = rot_elem(cs, half, rotate, to_float(part[e]), partner, e);
+        }
+        qo[i] = from_float<T>(v);
+    }
+}
+
+PL_EXPORT int pl_latent_q(const void* q_abs, const void* q, int dtype, int T, void* q_out, const int* positions,
+                          const int* token_seq, const float* table, int table_len, int rotary_dims, int nh, int d,
+                          int rot_dim, int kv_rank, int D, cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(nh > 0 && d > 0 && D >= kv_rank + rot_dim, "latent_q: bad sizes");
+    const int half = table != nullptr ? rotary_dims / 2 : 0;
+    if (dtype == PL_F32)
+        latent_q_kernel<float><<<T, 256, 0, stream>>>((const float*)q_abs, (const float*)q, (float*)q_out, positions,
+                                                      token_seq, (const float2*)table, table_len, half, nh, d, rot_dim,
+                                                      kv_rank, D);
+    else if (dtype == PL_BF16)
+        latent_q_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)q_abs, (const __nv_bfloat16*)q,
+                                                              (__nv_bfloat16*)q_out, positions, token_seq,
+                                                              (const float2*)table, table_len, half, nh, d, rot_dim,
+                                                              kv_rank, D);
+    else
+        return pl_fail("latent_q: unknown dtype %d", dtype);
+    PL_LAUNCHED("latent_q");
+    return 0;
+}

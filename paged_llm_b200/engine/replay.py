@@ -119,7 +119,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16)
-    ap.add_argument("--max-requests", type=int, default=64, help="most requests live at a time (state slots)")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     ap.add_argument("--enforce-eager", action="store_true", help="no CUDA-graph replay of decode steps")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)

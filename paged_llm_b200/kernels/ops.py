@@ -45,7 +45,7 @@ class AttnParams(ctypes.Structure):
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
         ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
         ("softcap", c_float), ("slopes", c_void_p), ("rope_table", c_void_p), ("rope_len", c_int),
-        ("pad_seqs", c_int), ("pad_to", c_int), ("chunk", c_int),
+        ("pad_seqs", c_int), ("pad_to", c_int), ("chunk", c_int), ("dist_bias", c_void_p), ("dist_len", c_int),
     ]
 
 
@@ -213,11 +213,12 @@ class CudaOps:
         return out
 
     # ---- embedding, norms, activation ------------------------------------------
-    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """Rows of `table` as the float32 stream, each element times `scale`."""
         T, (V, H) = ids.numel(), table.shape
         out = torch.empty((T, H), dtype=torch.float32, device=self.device)
         _check(self.core, self.core.pl_embedding(self._p(table), self._code(table), self._p(ids), self._p(out),
-                                                 T, H, V, self._stream))
+                                                 T, H, V, c_float(scale), self._stream))
         self.launches += 1
         return out
 
@@ -236,6 +237,28 @@ class CudaOps:
         bcode = self._code(branch) if branch is not None else PL_F32
         _check(self.core, self.core.pl_rmsnorm(self._p(x), self._p(branch), bcode, self._p(w), self._code(w),
                                                self._p(y), self._code(y), rows, H, c_float(eps), self._stream))
+        self.launches += 1
+        return y
+
+    def dyt(self, x: torch.Tensor | None, branch: torch.Tensor | None, post, pre, out_dtype=None):
+        """Dynamic tanh around the residual sum, one kernel: x += post(branch) in place (x the float32 stream),
+        then pre(x) in the compute dtype.  `post` and `pre` are (alpha, weight, bias) float32 tensors on the device or
+        None: without `post` the branch is added as it is; without `pre` nothing is returned.  With x None the result
+        is pre(post(branch)): a norm of a tensor that is not the stream."""
+        src = x if x is not None else branch
+        rows, H = src.shape
+        assert src.is_contiguous() and (x is None or x.dtype == torch.float32)
+        if branch is not None:
+            assert branch.shape == src.shape and branch.is_contiguous()
+        y = torch.empty((rows, H), dtype=out_dtype or self.compute_dtype, device=self.device) if pre is not None else None
+        po = post or (None, None, None)
+        pr = pre or (None, None, None)
+        for t in (*po, *pr):
+            assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+        _check(self.core, self.core.pl_dyt(self._p(x), self._p(branch), self._code(branch) if branch is not None else PL_F32,
+                                           self._p(po[0]), self._p(po[1]), self._p(po[2]), self._p(pr[0]), self._p(pr[1]),
+                                           self._p(pr[2]), self._p(y), self._code(y) if y is not None else PL_F32,
+                                           c_longlong(rows), H, self._stream))
         self.launches += 1
         return y
 
@@ -415,6 +438,122 @@ class CudaOps:
         self.launches += 1
         return qkv
 
+    # ---- mixers that are not plain grouped-query attention ----------------------------
+    def heads_linear(self, x: torch.Tensor, col0: int, head_stride: int, w: torch.Tensor) -> torch.Tensor:
+        """A product per head: out[t, h, :] = w[h] @ x[t, col0 + h * head_stride : ... + K] for w [heads, N, K];
+        returns [T, heads * N].  float32: this package's CUDA-core product, head by head on strided operands;
+        bfloat16: the library's batched product."""
+        T, ld = x.shape
+        nh, N, K = w.shape
+        assert x.is_contiguous() and w.is_contiguous() and col0 + (nh - 1) * head_stride + K <= ld and w.dtype == x.dtype
+        if x.dtype == torch.float32:
+            out = torch.empty((T, nh * N), dtype=torch.float32, device=self.device)
+            for h in range(nh):
+                _check(self.core, self.core.pl_gemm_f32(c_void_p(x.data_ptr() + 4 * (col0 + h * head_stride)),
+                                                        c_void_p(w.data_ptr() + 4 * h * N * K),
+                                                        c_void_p(out.data_ptr() + 4 * h * N), T, N, K, ld, K, nh * N,
+                                                        self._stream))
+                self.launches += 1
+            return out
+        xv = torch.as_strided(x, (nh, T, K), (head_stride, ld, 1), x.storage_offset() + col0)
+        return torch.bmm(xv, w.transpose(1, 2)).transpose(0, 1).reshape(T, nh * N)
+
+    def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
+                         write=True) -> torch.Tensor:
+        """proj rows [q: nh*d | k: nkv*d | v: nkv*dv | ...]: q and k are each divided by the root mean square
+        of the whole projection (all heads at once) and multiplied by their weights; returns the queries as
+        [T, nh*D] (heads padded to D with zeros) and writes keys and values, padded the same way, to their page
+        slots.  Without `has_kv` the rows hold no k and v (the layer reads another layer's cache)."""
+        T, ld = proj.shape
+        assert proj.is_contiguous() and kv.is_contiguous() and kv.dtype == proj.dtype and kv.shape[4] == D
+        q = torch.empty((T, nh * D), dtype=proj.dtype, device=self.device)
+        _check(self.core, self.core.pl_normed_qkv_write(
+            self._p(proj), self._code(proj), T, ld, self._p(q_weight), self._p(k_weight), c_float(eps), self._p(q),
+            self._p(kv), self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
+            kv.shape[0], kv.shape[3], nh, nkv, d, dv, D, 1 if has_kv else 0, 1 if write else 0, self._stream))
+        self.launches += 1
+        return q
+
+    def head_gate(self, o, nh, D, dv, gate=None) -> torch.Tensor:
+        """[T, nh*dv]: the first dv columns of each head of o [T, nh*D], times sigmoid(gate) if a gate
+        (a column view [T, nh*dv] of a row-major tensor) is given."""
+        T = o.shape[0]
+        assert o.is_contiguous() and o.shape[1] == nh * D
+        out = torch.empty((T, nh * dv), dtype=o.dtype, device=self.device)
+        ldg = 0
+        if gate is not None:
+            assert gate.dtype == o.dtype and gate.stride(1) == 1 and gate.shape == (T, nh * dv)
+            ldg = gate.stride(0)
+        _check(self.core, self.core.pl_head_gate(self._p(o), self._code(o), T, D, self._p(gate), ldg, self._p(out), nh, dv,
+                                                 self._stream))
+        self.launches += 1
+        return out
+
+    def latent_kv_write(self, down, q_rank, kv_rank, rot_dim, D, q_weight, c_weight, eps, position, ctx, kv, block_table,
+                        write=True) -> torch.Tensor:
+        """down rows [query latent: q_rank | key/value latent: kv_rank | rotated key part: rot_dim]: both latents
+        are RMS-normed (float32) with their weights; the normed query latent is returned [T, q_rank]; the cache
+        (one kv head of size D) gets the key [latent | rotated part | 0] and the value [latent | 0]."""
+        T, ld = down.shape
+        assert down.is_contiguous() and kv.is_contiguous() and kv.dtype == down.dtype and kv.shape[4] == D and kv.shape[2] == 1
+        cq = torch.empty((T, q_rank), dtype=down.dtype, device=self.device)
+        table = position.table if position is not None else None
+        _check(self.core, self.core.pl_latent_kv_write(
+            self._p(down), self._code(down), T, ld, self._p(q_weight), self._p(c_weight), c_float(eps), self._p(cq),
+            self._p(kv), self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
+            kv.shape[0], kv.shape[3], self._p(table), table.shape[0] if table is not None else 0,
+            position.rotary_dim if position is not None else 0, q_rank, kv_rank, rot_dim, D, 1 if write else 0,
+            self._stream))
+        self.launches += 1
+        return cq
+
+    def latent_queries(self, q_abs, q, nh, d, rot_dim, kv_rank, D, position, ctx) -> torch.Tensor:
+        """[T, nh*D] with head h = [q_abs[t, h] (kv_rank) | rotated q[t, h, d:d+rot_dim] | 0]."""
+        T = q.shape[0]
+        assert q.is_contiguous() and q_abs.is_contiguous() and q.shape[1] == nh * (d + rot_dim) and q_abs.shape[1] == nh * kv_rank
+        out = torch.empty((T, nh * D), dtype=q.dtype, device=self.device)
+        table = position.table if position is not None else None
+        _check(self.core, self.core.pl_latent_q(self._p(q_abs), self._p(q), self._code(q), T, self._p(out),
+                                                self._p(ctx.positions), self._p(ctx.token_seq), self._p(table),
+                                                table.shape[0] if table is not None else 0,
+                                                position.rotary_dim if position is not None else 0, nh, d, rot_dim, kv_rank,
+                                                D, self._stream))
+        self.launches += 1
+        return out
+
+    def ssm_mix(self, zx, inner, groups, state_size, heads, head_dim, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w,
+                norm_groups, eps, state, ctx) -> torch.Tensor:
+        """The state-space mixer between its two projections.  zx rows [z: inner | x: inner | B: G*N | C: G*N |
+        dt: heads] in the compute dtype; `state` [slots, (taps-1)*(inner+2GN) + heads*head_dim*N] float32 holds each
+        request's convolution inputs and recurrent state and is updated in place.  Returns the gated, normed
+        output [T, inner] in the compute dtype.  Three kernels: convolution + SiLU with dt and the decay;
+        the recurrence, token by token in float32; gate and norm in parts."""
+        lib = load_module("ssm")
+        T, ld = zx.shape
+        G, N, H, P = groups, state_size, heads, head_dim
+        C = inner + 2 * G * N
+        taps = conv_w.shape[1]
+        assert zx.is_contiguous() and ld == 2 * inner + 2 * G * N + H and state.dtype == torch.float32 and state.is_contiguous()
+        assert state.shape[1] == (taps - 1) * C + H * P * N
+        dev = self.device
+        xbc = torch.empty((T, C), dtype=torch.float32, device=dev)
+        dt = torch.empty((T, H), dtype=torch.float32, device=dev)
+        decay = torch.empty((T, H), dtype=torch.float32, device=dev)
+        y = torch.empty((T, inner), dtype=torch.float32, device=dev)
+        S = ctx.num_seqs
+        _check(lib, lib.pl_ssm_conv(self._p(zx), self._code(zx), ld, inner, C, 2 * inner + 2 * G * N, H, self._p(conv_w),
+                                    self._p(conv_b), taps, self._p(dt_bias), self._p(a_log), self._p(state),
+                                    c_longlong(state.shape[1]), self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S,
+                                    self._p(xbc), self._p(dt), self._p(decay), self._stream))
+        _check(lib, lib.pl_ssm_scan(self._p(xbc), C, inner, G, N, H, P, self._p(dt), self._p(decay), self._p(d_skip),
+                                    self._p(state), c_longlong(state.shape[1]), c_longlong((taps - 1) * C),
+                                    self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S, self._p(y), self._stream))
+        out = torch.empty((T, inner), dtype=zx.dtype, device=dev)
+        _check(lib, lib.pl_gated_group_norm(self._p(y), self._p(zx), self._code(zx), ld, self._p(norm_w), c_float(eps),
+                                            self._p(out), T, inner, norm_groups, self._p(ctx.token_seq), self._stream))
+        self.launches += 3
+        return out
+
     # ---- routed experts ----------------------------------------------------------
     def routed_experts(self, h, w_router, w_gate_up, w_down, top_k: int, activation: str = "silu", shared=None,
                        shared_activation: str = "silu") -> torch.Tensor:
@@ -589,11 +728,12 @@ class CudaOps:
                                     chunk=chunk)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
-                        rope=None, chunk=None):
+                        rope=None, chunk=None, dist_bias=None):
         """Attention of the step's tokens over the paged cache.  `softcap` (scores become
         softcap * tanh(score / softcap)) and `slopes` (a float32 tensor [nh]: head h adds
         slopes[h] * (key position - query position) to its scores) modify the scores; both off
-        by default; `chunk` c lets a query at position p see the keys from p - p % c on only.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
+        by default; `dist_bias` (float32 [nh, L]) adds dist_bias[h, min(query position - key position, L - 1)];
+        `chunk` c lets a query at position p see the keys from p - p % c on only.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
         `qkv_attention`): qkv is the unrotated projection, and the kernel rotates q and the step's own
         keys and writes those keys and values to the cache itself."""
         T = ctx.num_tokens
@@ -619,6 +759,10 @@ class CudaOps:
         if slopes is not None:
             assert slopes.dtype == torch.float32 and slopes.numel() == nh and slopes.is_contiguous() and slopes.is_cuda
             p.slopes = slopes.data_ptr()
+        if dist_bias is not None:
+            assert (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and dist_bias.shape[0] == nh
+                    and dist_bias.is_contiguous() and dist_bias.is_cuda)
+            p.dist_bias, p.dist_len = dist_bias.data_ptr(), dist_bias.shape[1]
         ps = kv.shape[3]
         p.ps_shift = ps.bit_length() - 1 if ps & (ps - 1) == 0 else -1
         p.counters = 0
@@ -629,7 +773,7 @@ class CudaOps:
             lib, fn = self.core, self.core.pl_attention_f32
         p.cluster = 0
         if rope is not None:
-            if not self._runs_as_clusters(plan, ctx, nh, nkv, bf16) or softcap or slopes is not None:
+            if not self._runs_as_clusters(plan, ctx, nh, nkv, bf16) or softcap or slopes is not None or dist_bias is not None:
                 raise KernelError("rotary positions inside the attention kernel: only for decode steps that run as "
                                   "clusters, without score modifiers")
             assert qkv.shape[1] == (nh + 2 * nkv) * d and rope.table.is_contiguous() and rope.rotary_dim == d

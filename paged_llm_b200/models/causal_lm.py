@@ -134,7 +134,7 @@ class CausalLM:
         rows = ops.gather_rows(x, ctx.logits_indices)
         if pending is None:
             rows_pending = None
-        elif isinstance(pending, LazyLinear):
+        elif hasattr(pending, "rows"):
             rows_pending = pending.rows(ops, ctx.logits_indices)     # the last projection runs on the wanted rows only
         else:
             rows_pending = ops.gather_rows(pending, ctx.logits_indices)

@@ -22,6 +22,8 @@ rotation (the cache still keeps both, since the stored key is rotated).
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import LazyLinear, Mixer, PagedKV, TensorSpec, register_mixer
@@ -96,4 +98,115 @@ class PagedAttention(Mixer):
         o = ops.qkv_attention(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position, ctx,
                               cache.kv, block_table, self.scale, self.window, write=cache.owner,
                               softcap=self.score_cap, slopes=self._slopes, **extra)
+        return LazyLinear(o, self.w_o)
+
+
+def log_distance_buckets(rows: int, far: float, length: int) -> list[int]:
+    """Row of a bias table for each distance 0 .. length-1: distances below rows // 2 have a row each; from there
+    on rows - rows // 2 rows are spaced evenly in the logarithm of the distance up to `far`; every distance whose
+    row would lie beyond the table shares the last row.  With h = rows // 2:
+    row(n) = n for n < h, else min(rows - 1, h + floor(ln(n / h) / ln(far / h) * (rows - h)))."""
+    half = rows // 2
+    out = []
+    for n in range(length):
+        if n < half:
+            out.append(n)
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
+
+
+def pad16(n: int) -> int:
+    return -(-n // 16) * 16
+
+
+@register_mixer("gated_attention")
+class GatedAttention(Mixer):
+    """Grouped-query attention over the paged cache with four things the plain part does not have:
+
+    * keys and values of different sizes (`head_dim`, `value_dim`); the cache and the attention kernel run at
+      the larger of the two rounded up to 16, the shorter vectors padded with zeros;
+    * a norm over the whole projection: q (all heads together) is divided by its root mean square and multiplied
+      by a weight of its size, and so is k; nothing is rotated;
+    * a learned bias by distance: the table `rel` [rows, heads] (as many rows as the checkpoint holds) is read at the row of `log_distance_buckets` and
+      added to the scaled score; it is laid out by distance once (`[heads, L]`) and the kernels read that;
+    * a sigmoid gate, computed from the mixer's input, on the concatenated heads in front of the output projection.
+
+    `window` w: the query at position p sees keys p-w+1 .. p.  `keep_window`: what the cache has to keep (the
+    largest window of the layers that read it; a layer with `shares_cache` has no key and value projections and
+    reads the cache of another layer, written with that layer's norm).
+    """
+
+    accepts_lazy_input = False
+
+    def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 value_dim: int, scale: float, eps: float, window: int | None = None, keep_window: int | None = 0,
+                 distance_bias: bool = False, bias_far: float = 0.0, bias_rows: int = 32, gate: bool = True,
+                 shares_cache: bool = False):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.value_dim, self.scale, self.eps = head_dim, value_dim, float(scale), float(eps)
+        self.window = int(window) if window else None
+        # (a layer without a window of its own keeps everything; else the larger of its window and what is asked)
+        self.keep_window = None if self.window is None or keep_window is None else max(int(keep_window), self.window)
+        # the table's number of rows is the checkpoint's (`bias_rows` only says how many the random-weights mode draws)
+        self.distance_bias, self.bias_far, self.bias_rows = bool(distance_bias), float(bias_far), int(bias_rows)
+        self.gate, self.shares_cache = bool(gate), bool(shares_cache)
+        self.cache_dim = pad16(max(head_dim, value_dim))
+        self.names = weights
+        self.w_in = self.w_o = self.q_weight = self.k_weight = self.bias_by_distance = None
+
+    def cache_requirement(self):
+        return PagedKV(self.num_kv_heads, self.cache_dim, self.keep_window)
+
+    def attention_plan_key(self):
+        return (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window, self.cache_dim)
+
+    def tensor_specs(self):
+        h, d, dv = self.hidden_size, self.head_dim, self.value_dim
+        out = {self.names["q_proj"]: TensorSpec((self.num_heads * d, h)),
+               self.names["q_norm"]: TensorSpec((self.num_heads * d,), role="vector", init="norm"),
+               self.names["o_proj"]: TensorSpec((h, self.num_heads * dv))}
+        if not self.shares_cache:
+            out[self.names["k_proj"]] = TensorSpec((self.num_kv_heads * d, h))
+            out[self.names["v_proj"]] = TensorSpec((self.num_kv_heads * dv, h))
+            out[self.names["k_norm"]] = TensorSpec((self.num_kv_heads * d,), role="vector", init="norm")
+        if self.distance_bias:
+            out[self.names["rel"]] = TensorSpec((-1, self.num_heads), role="vector", draw_shape=(self.bias_rows, self.num_heads))
+        if self.gate:
+            out[self.names["g_proj"]] = TensorSpec((self.num_heads * dv, h))
+        return out
+
+    def load(self, tensors):
+        stack = ["q_proj"] + ([] if self.shares_cache else ["k_proj", "v_proj"]) + (["g_proj"] if self.gate else [])
+        self.w_in = torch.cat([tensors[self.names[k]] for k in stack], dim=0).contiguous()
+        self.w_o = tensors[self.names["o_proj"]].contiguous()
+        self.q_weight = tensors[self.names["q_norm"]].float().contiguous()
+        self.k_weight = None if self.shares_cache else tensors[self.names["k_norm"]].float().contiguous()
+        if self.distance_bias:
+            rel = tensors[self.names["rel"]].float()
+            if rel.shape[0] < 2 or not self.bias_far > rel.shape[0] // 2:
+                raise ValueError(f"a bias table of {rel.shape[0]} rows needs at least two rows and a farthest distance "
+                                 f"above {rel.shape[0] // 2}, not {self.bias_far}")
+            # all distances from the farthest on share a row; no query reaches further back than its window
+            far = int(math.ceil(self.bias_far)) + 1
+            length = min(self.window, far) if self.window else far
+            rows = log_distance_buckets(rel.shape[0], self.bias_far, length)
+            self.bias_by_distance = rel[torch.tensor(rows, device=rel.device)].t().contiguous()      # [heads, length]
+
+    def bytes_read_per_step(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_o))
+
+    def forward(self, h, ctx, cache):
+        ops = ctx.ops
+        nh, nkv, d, dv, D = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.cache_dim
+        block_table = ctx.block_tables[cache.group]
+        proj = ops.linear(h, self.w_in)
+        q = ops.normed_qkv_write(proj, nh, nkv, d, dv, D, self.q_weight, self.k_weight, self.eps, ctx, cache.kv,
+                                 block_table, has_kv=not self.shares_cache, write=cache.owner and not self.shares_cache)
+        o = ops.paged_attention(q, nh, nkv, D, cache.kv, block_table, ctx, self.scale, self.window,
+                                dist_bias=self.bias_by_distance)
+        g0 = nh * d + (0 if self.shares_cache else nkv * (d + dv))
+        o = ops.head_gate(o, nh, D, dv, proj[:, g0:g0 + nh * dv] if self.gate else None)
         return LazyLinear(o, self.w_o)

@@ -82,6 +82,8 @@ class TensorSpec:
     init: how the random-weights mode draws it: "normal", "norm" (1 or 1+noise), "norm_zero" (0 or noise:
     a norm weight stored as its deviation from 1).
     optional: may be absent from the checkpoint (e.g. a tied head).
+    shape: an entry of -1 stands for a size that only the checkpoint gives (the rows of a table that
+    config.json does not state); `draw_shape` is then what the random-weights mode draws.
     """
 
     shape: tuple[int, ...]
@@ -89,6 +91,11 @@ class TensorSpec:
     init: str = "normal"
     optional: bool = False
     alias_of: str | None = None      # optional tensor that, when absent, is this other tensor
+    draw_shape: tuple[int, ...] | None = None
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(e == -1 or e == g for e, g in zip(self.shape, shape))
 
 
 # --------------------------------------------------------------------------- cache needs
@@ -136,8 +143,25 @@ class LazyLinear:
         return LazyLinear(ops.gather_rows(self.input, idx), self.weight)
 
 
+@dataclass
+class LazyNormed:
+    """A branch output whose own norm (`norm`, applied to the branch before it joins the stream) has not been
+    carried out yet.  The norm that consumes the branch may fuse it with the residual sum; anything else calls
+    `materialize`.  `branch` is a tensor or a `LazyLinear`."""
+
+    branch: object
+    norm: object
+
+    def materialize(self, ops) -> torch.Tensor:
+        return self.norm.apply(materialize(self.branch, ops), ops)
+
+    def rows(self, ops, idx: torch.Tensor) -> "LazyNormed":
+        b = self.branch
+        return LazyNormed(b.rows(ops, idx) if hasattr(b, "rows") else ops.gather_rows(b, idx), self.norm)
+
+
 def materialize(branch, ops):
-    return branch.materialize(ops) if isinstance(branch, LazyLinear) else branch
+    return branch.materialize(ops) if isinstance(branch, (LazyLinear, LazyNormed)) else branch
 
 
 # --------------------------------------------------------------------------- interfaces

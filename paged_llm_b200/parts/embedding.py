@@ -1,6 +1,6 @@
 """Token embedding and the output head.
 
-x[t] = E[ids[t]] with no scaling (reference: pagedllm/model/llama.py:191, :197);
+x[t] = E[ids[t]] (reference: pagedllm/model/llama.py:191, :197), times `scale` if a model gives one;
 logits = h W^T in float32, where W is E itself if the head is tied
 (llama.py:208-216).  A tied checkpoint may still carry the head's tensor; it is
 then ignored, as tying means the embedding is used.
@@ -13,8 +13,8 @@ from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 
 @register_embedding("embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int):
-        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+    def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int, scale: float = 1.0):
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
         self.name = weights["weight"]
         self.weight = None
 
@@ -25,6 +25,8 @@ class TokenEmbedding(Embedding):
         self.weight = tensors[self.name].contiguous()
 
     def forward(self, ids, ctx):
+        if self.scale != 1.0:
+            return ctx.ops.embedding(self.weight, ids, self.scale)      # (the stream is float32: the product is too)
         return ctx.ops.embedding(self.weight, ids)
 
 

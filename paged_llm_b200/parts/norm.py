@@ -6,7 +6,9 @@ the weights are taken."""
 
 from __future__ import annotations
 
-from .base import LazyLinear, Norm, TensorSpec, register_norm
+import torch
+
+from .base import LazyLinear, LazyNormed, Norm, TensorSpec, materialize, register_norm
 
 
 @register_norm("rms_norm")
@@ -35,3 +37,44 @@ class RMSNorm(Norm):
         if isinstance(branch, LazyLinear):
             return ctx.ops.linear_add_rms_norm(branch.input, branch.weight, x, self.weight, self.eps)
         return ctx.ops.add_rms_norm(x, branch, self.weight, self.eps)
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha x) * w + b: a norm that takes no mean and no variance of x.  `alpha` is one learned
+    number, w and b are vectors; all of it is elementwise and float32.  As the norm in front of a part it fuses
+    with the residual sum; as the norm behind a part (`LazyNormed`) it fuses in front of that sum, so that
+    x += behind(branch); h = front(x) is one kernel."""
+
+    def __init__(self, weights: dict[str, str], dim: int):
+        self.dim = dim
+        self.names = weights                  # weight, bias, alpha
+        self.params = None                    # (alpha [1], weight [dim], bias [dim]) float32
+
+    def tensor_specs(self):
+        return {self.names["weight"]: TensorSpec((self.dim,), role="vector", init="norm"),
+                self.names["bias"]: TensorSpec((self.dim,), role="vector", init="norm_zero"),
+                self.names["alpha"]: TensorSpec((), role="vector", init="norm")}
+
+    def load(self, tensors):
+        self.params = (tensors[self.names["alpha"]].float().reshape(1).contiguous(),
+                       tensors[self.names["weight"]].float().contiguous(),
+                       tensors[self.names["bias"]].float().contiguous())
+
+    def bytes_read_per_step(self):
+        return sum(t.numel() * 4 for t in self.params)
+
+    def apply(self, t: torch.Tensor, ops) -> torch.Tensor:
+        """The norm of a tensor that is not the stream, in the compute dtype."""
+        return ops.dyt(None, t, None, self.params)
+
+    def forward(self, x, ctx):
+        return ctx.ops.dyt(x, None, None, self.params)
+
+    def add_forward(self, x, branch, ctx):
+        if branch is None:
+            return self.forward(x, ctx)
+        ops = ctx.ops
+        if isinstance(branch, LazyNormed) and isinstance(branch.norm, DynamicTanh):
+            return ops.dyt(x, materialize(branch.branch, ops), branch.norm.params, self.params)
+        return ops.dyt(x, materialize(branch, ops), None, self.params)

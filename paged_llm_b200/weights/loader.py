@@ -125,7 +125,7 @@ def check_and_cast(expected: dict[str, TensorSpec], tensors: dict[str, torch.Ten
             if not spec.optional:
                 missing.append(name)
             continue
-        if tuple(tensors[name].shape) != tuple(spec.shape):
+        if not spec.fits(tensors[name].shape):
             wrong_shape.append((name, tuple(tensors[name].shape), tuple(spec.shape)))
         if not stored_dtype_ok(spec, tensors[name].dtype):
             wrong_dtype.append((name, str(tensors[name].dtype).replace("torch.", ""), spec.role,

@@ -46,12 +46,13 @@ def random_tensors(config: ModelConfig, seed: int = 0, std: float = 0.02, norm_s
             continue                                    # tied: not written
         if spec.role == "table_int":
             raise NotImplementedError(f"{name}: random integer tables are not defined")
+        shape = spec.draw_shape or spec.shape
         if spec.init in ("norm", "norm_zero"):        # norm weights: around one, or (stored as a deviation) around zero
-            t = torch.full(spec.shape, 1.0 if spec.init == "norm" else 0.0, dtype=torch.float32)
+            t = torch.full(shape, 1.0 if spec.init == "norm" else 0.0, dtype=torch.float32)
             if norm_std:
-                t = t + norm_std * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+                t = t + norm_std * torch.randn(shape, generator=gen, dtype=torch.float32)
         else:
-            t = std * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+            t = std * torch.randn(shape, generator=gen, dtype=torch.float32)
         out[name] = t.to(_DTYPES[dtype]).contiguous()
     return out
 
@@ -116,15 +117,16 @@ def draw_on_device(expected: dict, stub: dict, compute: torch.dtype, device, ops
             continue
         if spec.role == "table_int":
             raise NotImplementedError(f"{name}: random integer tables are not defined")
+        shape = spec.draw_shape or spec.shape
         if spec.init in ("norm", "norm_zero"):
             centre = 1.0 if spec.init == "norm" else 0.0
-            t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+            t = torch.empty(shape, dtype=torch.float32, device=device)
             if stub["norm_std"]:
                 ops.fill_normal(t, stub["seed"], tensor_key(name), centre, stub["norm_std"])
             else:
                 t.fill_(centre)
         else:
-            t = torch.empty(spec.shape, dtype=compute, device=device)
+            t = torch.empty(shape, dtype=compute, device=device)
             ops.fill_normal(t, stub["seed"], tensor_key(name), 0.0, stub["std"])
         out[name] = t
     return out

@@ -29,9 +29,24 @@ class TorchOps:
         self.compute_dtype = dtype
 
     # ---- elementwise / norms ---------------------------------------------------
-    def embedding(self, table, ids):
+    def embedding(self, table, ids, scale=1.0):
         self._count("embedding")
-        return table[ids.long()].float()
+        return table[ids.long()].float() * scale
+
+    def dyt(self, x, branch, post, pre, out_dtype=None):
+        self._count("dyt")
+        v = None
+        if branch is not None:
+            v = branch.float()
+            if post is not None:
+                v = torch.tanh(post[0] * v) * post[1] + post[2]
+        if x is not None:
+            if v is not None:
+                x += v
+            v = x
+        if pre is None:
+            return None
+        return (torch.tanh(pre[0] * v) * pre[1] + pre[2]).to(out_dtype or self.compute_dtype)
 
     def rms_norm(self, x, w, eps):
         self._count("rms_norm")
@@ -155,7 +170,7 @@ class TorchOps:
                               pad_tokens=pad_tokens)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
-                        chunk=None):
+                        chunk=None, dist_bias=None):
         self._count("paged_attention")
         T = ctx.num_tokens
         q = qkv[:, :nh * d].view(T, nh, d).float()
@@ -182,6 +197,9 @@ class TorchOps:
                 scores = softcap * torch.tanh(scores / softcap)
             if slopes is not None:
                 scores = scores + slopes.float().cpu()[:, None, None] * (idx[None, None, :] - qpos[None, :, None])
+            if dist_bias is not None:
+                dist = (qpos[:, None] - idx[None, :]).clamp(0, dist_bias.shape[1] - 1)
+                scores = scores + dist_bias.float().cpu()[:, dist]
             hidden = idx[None, :] > qpos[:, None]
             if window:
                 hidden |= idx[None, :] <= qpos[:, None] - window
@@ -191,6 +209,136 @@ class TorchOps:
             o = torch.einsum("hqk,khd->qhd", scores.softmax(-1), v)
             out[cu[s]:cu[s + 1]] = o.reshape(nq, nh * d).to(self.compute_dtype)
         return out
+
+    # ---- mixers that are not plain grouped-query attention -----------------------
+    def _write_slots(self, ctx, kv, block_table, k, v):
+        """k, v: [T, heads, D] into the page slots of the step's tokens."""
+        ps = kv.shape[3]
+        seq, pos = ctx.token_seq.long(), ctx.positions.long()
+        for t in range(k.shape[0]):
+            if seq[t] < 0:
+                continue
+            p = int(pos[t])
+            page = int(block_table[seq[t], p // ps])
+            assert page >= 0, "write into a page that was given back"
+            kv[page, 0, :, p % ps, :] = k[t].to(kv.dtype)
+            kv[page, 1, :, p % ps, :] = v[t].to(kv.dtype)
+
+    def heads_linear(self, x, col0, head_stride, w):
+        self._count("heads_linear")
+        nh, N, K = w.shape
+        xs = torch.stack([x[:, col0 + h * head_stride:col0 + h * head_stride + K] for h in range(nh)], dim=1).float()
+        return torch.einsum("thk,hnk->thn", xs, w.float()).reshape(x.shape[0], nh * N).to(self.compute_dtype)
+
+    def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
+                         write=True):
+        self._count("normed_qkv_write")
+        T = proj.shape[0]
+        pf = proj.float()
+
+        def normed(x, w):
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+        q = torch.zeros(T, nh, D)
+        q[:, :, :d] = normed(pf[:, :nh * d], q_weight).view(T, nh, d)
+        if has_kv and write:
+            k = torch.zeros(T, nkv, D)
+            v = torch.zeros(T, nkv, D)
+            k[:, :, :d] = normed(pf[:, nh * d:(nh + nkv) * d], k_weight).view(T, nkv, d)
+            v[:, :, :dv] = pf[:, (nh + nkv) * d:(nh + nkv) * d + nkv * dv].view(T, nkv, dv)
+            self._write_slots(ctx, kv, block_table, k, v)
+        return q.reshape(T, nh * D).to(self.compute_dtype)
+
+    def head_gate(self, o, nh, D, dv, gate=None):
+        self._count("head_gate")
+        T = o.shape[0]
+        out = o.float().view(T, nh, D)[:, :, :dv].reshape(T, nh * dv)
+        if gate is not None:
+            out = out * torch.sigmoid(gate.float())
+        return out.to(self.compute_dtype)
+
+    @staticmethod
+    def _rotate_pairs(x, position, pos):
+        """x [T, ..., n]: pairs (2i, 2i+1) of the first rotary_dim elements."""
+        if position is None:
+            return x
+        rd = position.rotary_dim
+        cs = position.table[pos]                            # [T, rd/2, 2]
+        shape = [cs.shape[0]] + [1] * (x.dim() - 2) + [rd // 2]
+        cos, sin = cs[..., 0].view(shape), cs[..., 1].view(shape)
+        a, b = x[..., 0:rd:2], x[..., 1:rd:2]
+        out = x.clone()
+        out[..., 0:rd:2] = a * cos - b * sin
+        out[..., 1:rd:2] = b * cos + a * sin
+        return out
+
+    def latent_kv_write(self, down, q_rank, kv_rank, rot_dim, D, q_weight, c_weight, eps, position, ctx, kv, block_table,
+                        write=True):
+        self._count("latent_kv_write")
+        T = down.shape[0]
+        df = down.float()
+
+        def normed(x, w):
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+        cq = normed(df[:, :q_rank], q_weight).to(self.compute_dtype)
+        if write:
+            c = normed(df[:, q_rank:q_rank + kv_rank], c_weight).to(self.compute_dtype).float()
+            kr = self._rotate_pairs(df[:, q_rank + kv_rank:], position, ctx.positions.long())
+            k = torch.zeros(T, 1, D)
+            v = torch.zeros(T, 1, D)
+            k[:, 0, :kv_rank] = c
+            k[:, 0, kv_rank:kv_rank + rot_dim] = kr
+            v[:, 0, :kv_rank] = c
+            self._write_slots(ctx, kv, block_table, k, v)
+        return cq
+
+    def latent_queries(self, q_abs, q, nh, d, rot_dim, kv_rank, D, position, ctx):
+        self._count("latent_queries")
+        T = q.shape[0]
+        out = torch.zeros(T, nh, D)
+        out[:, :, :kv_rank] = q_abs.float().view(T, nh, kv_rank)
+        qr = q.float().view(T, nh, d + rot_dim)[:, :, d:]
+        out[:, :, kv_rank:kv_rank + rot_dim] = self._rotate_pairs(qr, position, ctx.positions.long())
+        return out.reshape(T, nh * D).to(self.compute_dtype)
+
+    def ssm_mix(self, zx, inner, groups, state_size, heads, head_dim, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w,
+                norm_groups, eps, state, ctx):
+        self._count("ssm_mix")
+        G, N, H, P = groups, state_size, heads, head_dim
+        C = inner + 2 * G * N
+        taps = conv_w.shape[1]
+        hist = taps - 1
+        zf = zx.float()
+        out = torch.zeros(zx.shape[0], inner)
+        cu = ctx.host.cu
+        for s, slot in enumerate(ctx.host.state_slots):
+            assert slot >= 0, "a request of a model with state must own a slot"
+            rows = zf[cu[s]:cu[s + 1]]
+            nq = rows.shape[0]
+            st = state[slot]
+            old = st[:hist * C].view(hist, C)
+            S = st[hist * C:].view(H, P, N)
+            seq = torch.cat([old, rows[:, inner:inner + C]], dim=0)           # [hist + nq, C]
+            xbc = conv_b[None, :].expand(nq, C).clone()
+            for k in range(taps):
+                xbc = xbc + seq[k:k + nq] * conv_w[:, k][None, :]
+            xbc = xbc * torch.sigmoid(xbc)
+            old.copy_(seq[nq:nq + hist].clone())
+            dt = torch.nn.functional.softplus(rows[:, 2 * inner + 2 * G * N:] + dt_bias[None, :])
+            decay = torch.exp(-torch.exp(a_log)[None, :] * dt)
+            x = xbc[:, :inner].view(nq, H, P)
+            B = xbc[:, inner:inner + G * N].view(nq, G, N).repeat_interleave(H // G, dim=1)
+            Cm = xbc[:, inner + G * N:].view(nq, G, N).repeat_interleave(H // G, dim=1)
+            y = torch.zeros(nq, H, P)
+            for t in range(nq):
+                S.mul_(decay[t][:, None, None]).add_(dt[t][:, None, None] * x[t][:, :, None] * B[t][:, None, :])
+                y[t] = torch.einsum("hpn,hn->hp", S, Cm[t]) + d_skip[:, None] * x[t]
+            v = y.view(nq, inner) * (rows[:, :inner] * torch.sigmoid(rows[:, :inner]))
+            v = v.view(nq, norm_groups, inner // norm_groups)
+            v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+            out[cu[s]:cu[s + 1]] = v.reshape(nq, inner) * norm_w[None, :]
+        return out.to(self.compute_dtype)
 
     def copy_pages(self, pool, pairs):
         self._count("copy_pages")
