@@ -73,6 +73,18 @@ POMISUN_SIZES = {
     "p-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, experts=4, top=2, expert_ff=64,
                    shared_ff=64, chunk=64, layers=2, loop=None),
 }
+# Layer sizes for `--only rokarax`: the Rokarax decoder (state-space layers, windowed attention with a bias by distance
+# and an output gate, one of them reading the other's keys and values, and attention through latents) beside a Llama of
+# the same width, heads, head size, dense inner size and number of layers.
+ROKARAX_SIZES = {
+    "r-2k": dict(vocab=32000, width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, q_rank=768, kv_rank=192,
+                 rot_dim=64, ssm_heads=64, ssm_dim=64, state=128, groups=1, conv=4),
+    "r-4k": dict(vocab=32000, width=4096, heads=32, kv_heads=8, dim=128, ff=14336, window=2048, q_rank=1536, kv_rank=192,
+                 rot_dim=64, ssm_heads=128, ssm_dim=64, state=128, groups=1, conv=4),
+    # for trying the option out quickly; never a result
+    "r-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, window=64, q_rank=48, kv_rank=32,
+                   rot_dim=16, ssm_heads=8, ssm_dim=16, state=16, groups=2, conv=3),
+}
 PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
 RAGGED_PROMPTS, RAGGED_OUTPUTS = (128, 4096), (64, 512)      # the ragged serving workload: lengths drawn uniformly
 
@@ -236,6 +248,8 @@ def device_decode_loop(engine, batch: int, steps: int, warmup: int, prompt_len: 
     vocab = engine.model_config.vocab_size
     seqs = [Sequence(p, SamplingParams(temperature=0.0, max_tokens=steps + warmup + 2))
             for p in prompts_for(vocab, batch, prompt_len, seed=batch)]
+    for s in seqs:
+        assert cm.acquire_state_slot(s), "too few state slots for the benchmark"      # (models with state of fixed size)
     chunk = max(1, engine.config.max_num_batched_tokens // prompt_len)
     for i in range(0, batch, chunk):
         group = seqs[i:i + chunk]
@@ -309,7 +323,7 @@ def decode_kernel_times(engine, batch: int, steps: int, warmup: int, prompt_len:
         per_step[name] += 1
         total[name] += e.time_range.end - e.time_range.start
     return {k: [round(per_step[k] / steps, 1), round(total[k] / per_step[k], 2)]
-            for k in sorted(total, key=lambda k: -total[k])[:14]}
+            for k in sorted(total, key=lambda k: -total[k])[:24]}
 
 
 def prefill_kernel_times(engine, tokens: int) -> dict:
@@ -330,7 +344,7 @@ def prefill_kernel_times(engine, tokens: int) -> dict:
         name = name.split("(")[0][:72]
         count[name] += 1
         total[name] += e.time_range.end - e.time_range.start
-    return {k: [count[k], round(total[k] / count[k], 2)] for k in sorted(total, key=lambda k: -total[k])[:14]}
+    return {k: [count[k], round(total[k] / count[k], 2)] for k in sorted(total, key=lambda k: -total[k])[:24]}
 
 
 def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
@@ -403,6 +417,7 @@ def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
     times = []
     for i in range(warmup + iters):
         seq = Sequence(prompts_for(vocab, 1, tokens, seed=7 + i)[0], SamplingParams())
+        assert cm.acquire_state_slot(seq), "too few state slots for the benchmark"
         ok = cm.allocate_slots(seq, tokens)
         assert ok is not None, "pool too small for the benchmark"
         torch.cuda.synchronize()
@@ -429,6 +444,8 @@ def mixed_step(engine, batch: int, portion: int, context: int, iters: int = 5, w
     cm, runner, ops = engine.block_manager, engine.runner, engine.ops
     vocab = engine.model_config.vocab_size
     seqs = [Sequence(p, SamplingParams()) for p in prompts_for(vocab, batch, context, seed=3)]
+    for s in seqs:
+        assert cm.acquire_state_slot(s), "too few state slots for the benchmark"
     chunk = max(1, engine.config.max_num_batched_tokens // context)
     for i in range(0, batch, chunk):
         group = seqs[i:i + chunk]
@@ -442,6 +459,7 @@ def mixed_step(engine, batch: int, portion: int, context: int, iters: int = 5, w
     times = []
     for i in range(warmup + iters):
         new = Sequence(prompts_for(vocab, 1, portion, seed=50 + i)[0], SamplingParams())
+        assert cm.acquire_state_slot(new), "too few state slots for the benchmark"
         ok = cm.allocate_slots(new, portion)
         assert ok is not None
         for s in seqs:
@@ -584,8 +602,30 @@ def pomisun_configs(name: str):
     return pom, llama, runs
 
 
-def pomisun_compare(args) -> dict:
-    """Prefill and decode of the Pomisun decoder at layer sizes of a real model (random weights drawn on the
+def rokarax_configs(name: str):
+    """(Rokarax configuration dict, Llama configuration dict of equal size, number of layers)."""
+    s = ROKARAX_SIZES[name]
+    attention = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                 "bias_max": float(s["window"]), "mask": {"size": s["window"]}}
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["dim"], "q_rank": s["q_rank"],
+              "kv_rank": s["kv_rank"], "scale": (s["dim"] + s["rot_dim"]) ** -0.5, "mask": {"size": s["window"]},
+              "rot": {"dims": s["rot_dim"], "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    ssm = {"heads": s["ssm_heads"], "vdim": s["ssm_dim"], "state": s["state"], "groups": s["groups"], "conv": s["conv"],
+           "norm_groups": s["groups"]}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    order = [("mamba2", ssm), ("attention", attention), ("mamba2", ssm), ("latent_attention", latent), ("mamba2", ssm),
+             ("attention", dict(attention, kv_from=1))]
+    rok = {"architecture": "Rokarax", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": s["width"] ** 0.5},
+           "norm": {"eps": 1e-6}, "layers": [{"type": t, "mixer": m, "mlp": dense} for t, m in order]}
+    llama = {"architectures": ["LlamaForCausalLM"], "vocab_size": s["vocab"], "hidden_size": s["width"],
+             "intermediate_size": s["ff"], "num_hidden_layers": len(order), "num_attention_heads": s["heads"],
+             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 500000.0, "rms_norm_eps": 1e-6,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192}
+    return rok, llama, len(order)
+
+
+def compare_with_llama(args, label: str, size: str, sizes: dict, model: dict, llama: dict, runs: int) -> dict:
+    """Prefill and decode of another decoder at layer sizes of a real model (random weights drawn on the
     device) beside a Llama of equal width, heads and layer runs: device-timed with CUDA events, with the device
     time of every kernel inside the steps for the roofline of each."""
     import torch
@@ -593,15 +633,14 @@ def pomisun_compare(args) -> dict:
     from paged_llm_b200.config.registry import parse_model_config
     from paged_llm_b200.weights import write_random_stub
 
-    pom, llama, runs = pomisun_configs(args.pomisun_size)
     pre = args.prefill_tokens or PREFILL_TOKENS
     ctx_len = args.context or PROMPT_LEN
     steps = min(args.steps, 64)
     batches = (8, 64) if args.batch == 8 else (args.batch,)
     max_len = max(ctx_len + steps + args.warmup + 16, pre) + 64
-    out = {"only": "pomisun", "size": args.pomisun_size, "layer_runs": runs, "prefill_tokens": pre, "context": ctx_len,
-           "sizes": POMISUN_SIZES[args.pomisun_size], "peaks": load_peaks()}
-    for arm, hf in (("pomisun", pom), ("llama", llama)):
+    out = {"only": label, "size": size, "layer_runs": runs, "prefill_tokens": pre, "context": ctx_len,
+           "sizes": sizes, "peaks": load_peaks()}
+    for arm, hf in ((label, model), ("llama", llama)):
         with tempfile.TemporaryDirectory() as folder:
             _, cfg = parse_model_config(hf)
             write_random_stub(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
@@ -629,6 +668,16 @@ def pomisun_compare(args) -> dict:
     return out
 
 
+def pomisun_compare(args) -> dict:
+    pom, llama, runs = pomisun_configs(args.pomisun_size)
+    return compare_with_llama(args, "pomisun", args.pomisun_size, POMISUN_SIZES[args.pomisun_size], pom, llama, runs)
+
+
+def rokarax_compare(args) -> dict:
+    rok, llama, runs = rokarax_configs(args.rokarax_size)
+    return compare_with_llama(args, "rokarax", args.rokarax_size, ROKARAX_SIZES[args.rokarax_size], rok, llama, runs)
+
+
 def run_ours(args) -> dict:
     import torch
     from paged_llm_b200 import EngineConfig, LLMEngine
@@ -636,6 +685,8 @@ def run_ours(args) -> dict:
     peaks = load_peaks()
     if args.only == "pomisun":
         return pomisun_compare(args)
+    if args.only == "rokarax":
+        return rokarax_compare(args)
     if args.only == "validate":
         return validate(args)
     if args.only == "sample":
@@ -830,11 +881,14 @@ def main() -> int:
                     help="with --only decode or --only prefill: add the device time of every kernel inside the replayed steps")
     ap.add_argument("--pomisun-size", choices=sorted(POMISUN_SIZES), default="p-2k",
                     help="with --only pomisun: the layer sizes (the Llama beside it gets the same)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun"], default=None,
+    ap.add_argument("--rokarax-size", choices=sorted(ROKARAX_SIZES), default="r-2k",
+                    help="with --only rokarax: the layer sizes (the Llama beside it gets the same)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun", "rokarax"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
                          "portion of --prefill-tokens), the float32 validation run, the sampler's kernels on --batch rows, or "
-                         "prefill and decode of the Pomisun decoder beside a Llama of equal size (--pomisun-size), and print "
+                         "prefill and decode of the Pomisun or the Rokarax decoder beside a Llama of equal size (--pomisun-size, "
+                         "--rokarax-size), and print "
                          "a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:

@@ -246,21 +246,14 @@ class RokaraxConfig(ModelConfig):
 
     @property
     def num_parameters(self) -> int:
-        w = self.hidden_size
-        total = 2 * self.vocab_size * w + 2 * w + 1
-        for lay in self.layers:
-            m = lay.mixer
-            total += 2 * (2 * w + 1)
-            if lay.type == "attention":
-                total += 2 * m.heads * m.dim * w + m.heads * m.dim + 2 * m.heads * m.vdim * w
-                if m.kv_from is None:
-                    total += m.kv_heads * (m.dim + m.vdim) * w + m.kv_heads * m.dim
-            elif lay.type == "latent_attention":
-                total += (m.q_rank + m.kv_rank + m.rot_dim) * w + m.q_rank + m.kv_rank
-                total += m.heads * (m.dim + m.rot_dim) * m.q_rank + m.heads * (m.dim + m.vdim) * m.kv_rank + m.heads * m.vdim * w
-            else:
-                inner, ch = m.heads * m.vdim, m.heads * m.vdim + 2 * m.groups * m.state
-                total += (inner + ch + m.heads) * w + ch * (m.conv + 1) + 3 * m.heads + inner + inner * w
-            if lay.ff is not None:
-                total += 2 * (2 * w + 1) + 3 * lay.ff * w
+        """Counted from the tensors the model expects (a bias table with the rows random weights are drawn with)."""
+        from ..models.causal_lm import build_model
+        from ..models.rokarax import rokarax_spec
+
+        total = 0
+        for spec in build_model(rokarax_spec(self)).tensor_specs().values():
+            n = 1
+            for e in spec.draw_shape or spec.shape:
+                n *= e
+            total += n
         return total

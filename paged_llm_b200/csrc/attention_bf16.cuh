@@ -673,8 +673,9 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     // prompt portions of head sizes 64 and 128 with a cap on the scores (and no bias by distance): the
     // tcgen05 kernel applies the cap itself
     static const bool no_tc_cap = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
-    if (p.softcap > 0.f && p.slopes == nullptr && p.dist_bias == nullptr && p.rope_table == nullptr && p.cluster <= 0 && !p.is_small &&
-        p.d == PL_DPAD && !no_tc_cap && tc2::takes(p))
+    // (and so it does a bias by distance, read from its table per score)
+    if ((p.softcap > 0.f || p.dist_bias != nullptr) && p.slopes == nullptr && p.rope_table == nullptr && p.cluster <= 0 &&
+        !p.is_small && p.d == PL_DPAD && !no_tc_cap && tc2::takes(p) && p.scale > 0.f)
         return tc2::launch<PL_DPAD>(p, stream);
 #endif
     PL_REQUIRE(p.dist_bias == nullptr || p.dist_len > 0, "attention_bf16: a bias by distance of %d entries", p.dist_len);

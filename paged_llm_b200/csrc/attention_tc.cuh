@@ -573,6 +573,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         const bool capped = p.softcap > 0.f;
         const float cap_in = capped ? 2.f * 1.4426950408889634f * p.scale / p.softcap : 0.f;
         const float cap_out = capped ? p.softcap / p.scale : 0.f;
+        const float* bias_row = p.dist_bias != nullptr && R < it.rows_total
+                                    ? p.dist_bias + (size_t)(kvh * G + R % G) * p.dist_len : nullptr;
+        const float bias_unit = 1.f / p.scale;
         float m_run = -INFINITY, l_run = 0.f;
         float sv[64];
         for (int t = 0; t < n_tiles; ++t) {
@@ -589,6 +592,14 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                     asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(1.f + ex2(sv[i] * cap_in)));
                     sv[i] = fmaf(-2.f * cap_out, r, cap_out);
                 }
+            }
+            if (bias_row != nullptr) {
+                // a learned bias by distance, brought into the units of the raw product (the scale comes below); a
+                // key behind the query reads entry 0 and is masked below
+                const int far = p.dist_len - 1;
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    sv[i] = fmaf(__ldg(bias_row + min(max(pos - kbase - i, 0), far)), bias_unit, sv[i]);
             }
             const bool row_full = kbase >= it.key_lo && kbase >= first && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
             const bool warp_full = __all_sync(0xffffffffu, row_full);

@@ -45,9 +45,78 @@ __global__ void dyt_kernel(float* __restrict__ x, const TB* __restrict__ branch,
     }
 }
 
+// The same with four columns per thread: grid (column quads / 256, row groups); a thread keeps the norms' weights
+// of its four columns in registers and walks the rows.
+template <typename T> struct Quad4;
+template <> struct Quad4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Quad4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+__device__ __forceinline__ float4 dyt4(float4 v, float a, float4 w, float4 b) {
+    return make_float4(fmaf(tanhf(a * v.x), w.x, b.x), fmaf(tanhf(a * v.y), w.y, b.y), fmaf(tanhf(a * v.z), w.z, b.z),
+                       fmaf(tanhf(a * v.w), w.w, b.w));
+}
+
+template <typename TB, typename TY>
+__global__ void __launch_bounds__(256) dyt4_kernel(float* __restrict__ x, const TB* __restrict__ branch, DytParams post,
+                                                   DytParams pre, TY* __restrict__ y, int rows, int H) {
+    pdl_launch_dependents();
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (c >= H) return;
+    // (the norms' parameters are weights: older than the kernel in front)
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float a_post = post.alpha != nullptr ? __ldg(post.alpha) : 0.f;
+    const float a_pre = pre.alpha != nullptr ? __ldg(pre.alpha) : 0.f;
+    const float4 w1 = post.alpha != nullptr ? Quad4<float>::load(post.w + c) : zero;
+    const float4 b1 = post.alpha != nullptr ? Quad4<float>::load(post.b + c) : zero;
+    const float4 w2 = pre.alpha != nullptr ? Quad4<float>::load(pre.w + c) : zero;
+    const float4 b2 = pre.alpha != nullptr ? Quad4<float>::load(pre.b + c) : zero;
+    pdl_wait();
+    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+        const size_t i = (size_t)r * H + c;
+        float4 v = zero;
+        if (branch != nullptr) {
+            v = Quad4<TB>::load(branch + i);
+            if (post.alpha != nullptr) v = dyt4(v, a_post, w1, b1);
+        }
+        if (x != nullptr) {
+            const float4 s = Quad4<float>::load(x + i);
+            v = make_float4(v.x + s.x, v.y + s.y, v.z + s.z, v.w + s.w);
+            if (branch != nullptr) Quad4<float>::store(x + i, v);
+        }
+        if (y != nullptr) Quad4<TY>::store(y + i, dyt4(v, a_pre, w2, b2));
+    }
+}
+
 template <typename TB, typename TY>
 static int launch_dyt(float* x, const void* branch, DytParams post, DytParams pre, void* y, long long n, int H,
                       cudaStream_t stream) {
+    const long long rows = n / H;
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (H % 4 == 0 && rows < (1ll << 31) && aligned(x) && aligned(branch) && aligned(y) && aligned(post.w) && aligned(post.b) &&
+        aligned(pre.w) && aligned(pre.b)) {
+        const int bx = (H / 4 + 255) / 256;
+        const long long by = rows < 65535 ? rows : 65535;
+        PL_CUDA(launch_pdl(dyt4_kernel<TB, TY>, dim3(bx, (unsigned)by), dim3(256), 0, stream, x, (const TB*)branch, post, pre,
+                           (TY*)y, (int)rows, H));
+        return 0;
+    }
     const long long blocks = (n + 255) / 256;
     PL_CUDA(launch_pdl(dyt_kernel<TB, TY>, dim3((unsigned)(blocks < 4096 ? blocks : 4096)), dim3(256), 0, stream, x,
                        (const TB*)branch, post, pre, (TY*)y, n, H));
@@ -95,7 +164,7 @@ __device__ __forceinline__ long long key_slot(const SlotArgs& a, int t, int s, i
 template <typename T>
 __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ qw,
                                   const float* __restrict__ kw, float eps, T* __restrict__ q_out, T* __restrict__ kv,
-                                  SlotArgs sa, int nh, int nkv, int d, int dv, int D, int has_kv, int write) {
+                                  SlotArgs sa, int nh, int nkv, int d, int dv, int D, int has_kv, int write, int vec) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int s = sa.token_seq[t];
@@ -112,9 +181,21 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
         sq += v * v;
     }
     const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
-    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
-        const int h = i / D, c = i - h * D;
-        qo[i] = from_float<T>(c < d ? to_float(row[h * d + c]) * rq * __ldg(qw + h * d + c) : 0.f);
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < nh * D; i += blockDim.x * 4) {
+            const int h = i / D, c = i - h * D;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < d) {
+                const float4 a = Quad4<T>::load(row + h * d + c), w = Quad4<float>::load(qw + h * d + c);
+                v = make_float4(a.x * rq * w.x, a.y * rq * w.y, a.z * rq * w.z, a.w * rq * w.w);
+            }
+            Quad4<T>::store(qo + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+            const int h = i / D, c = i - h * D;
+            qo[i] = from_float<T>(c < d ? to_float(row[h * d + c]) * rq * __ldg(qw + h * d + c) : 0.f);
+        }
     }
     if (!has_kv || !write) return;
     const long long slot = key_slot(sa, t, s, sa.positions[t], nkv, D);
@@ -126,6 +207,20 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
     const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
     if (slot < 0) return;
     const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < nkv * D; i += blockDim.x * 4) {
+            const int h = i / D, c = i - h * D;
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (c < d) {
+                const float4 a = Quad4<T>::load(row + nq + h * d + c), w = Quad4<float>::load(kw + h * d + c);
+                kk = make_float4(a.x * rk * w.x, a.y * rk * w.y, a.z * rk * w.z, a.w * rk * w.w);
+            }
+            if (c < dv) vv = Quad4<T>::load(row + nq + nk + h * dv + c);
+            Quad4<T>::store(kv + slot + h * head_stride + c, kk);
+            Quad4<T>::store(kv + slot + v_off + h * head_stride + c, vv);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
         const int h = i / D, c = i - h * D;
         const float kk = c < d ? to_float(row[nq + h * d + c]) * rk * __ldg(kw + h * d + c) : 0.f;
@@ -143,13 +238,16 @@ PL_EXPORT int pl_normed_qkv_write(const void* proj, int dtype, int T, int ld, co
     PL_REQUIRE(nh > 0 && nkv > 0 && d > 0 && dv > 0 && D >= d && D >= dv, "normed_qkv_write: bad head sizes d=%d dv=%d D=%d", d,
                dv, D);
     SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
+    // four elements per step where every head, row and pointer allows it
+    const int vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 &&
+                    (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
     if (dtype == PL_F32)
         normed_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, qw, kw, eps, (float*)q_out, (float*)kv, sa,
-                                                        nh, nkv, d, dv, D, has_kv, write);
+                                                        nh, nkv, d, dv, D, has_kv, write, vec);
     else if (dtype == PL_BF16)
         normed_qkv_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, qw, kw, eps,
                                                                 (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv, sa, nh, nkv,
-                                                                d, dv, D, has_kv, write);
+                                                                d, dv, D, has_kv, write, vec);
     else
         return pl_fail("normed_qkv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("normed_qkv_write");
@@ -174,22 +272,48 @@ __global__ void head_gate_kernel(const T* __restrict__ o, int D, const T* __rest
     }
 }
 
+// The same, four elements per thread: grid (quads of a row / 256, row groups).
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate4_kernel(const T* __restrict__ o, int D, const T* __restrict__ gate, int ldg,
+                                                         T* __restrict__ out, int rows, int nh, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (e >= nh * dv) return;
+    const int h = e / dv, c = e - h * dv;
+    for (int t = blockIdx.y; t < rows; t += gridDim.y) {
+        float4 v = Quad4<T>::load(o + (size_t)t * nh * D + h * D + c);
+        if (gate != nullptr) {
+            const float4 g = Quad4<T>::load(gate + (size_t)t * ldg + e);
+            v = make_float4(v.x / (1.0f + expf(-g.x)), v.y / (1.0f + expf(-g.y)), v.z / (1.0f + expf(-g.z)),
+                            v.w / (1.0f + expf(-g.w)));
+        }
+        Quad4<T>::store(out + (size_t)t * nh * dv + e, v);
+    }
+}
+
+template <typename T>
+static int launch_head_gate(const void* o, int T_, int D, const void* gate, int ldg, void* out, int nh, int dv,
+                            cudaStream_t stream) {
+    if (dv % 4 == 0 && D % 4 == 0 && ldg % 4 == 0 && (((uintptr_t)o | (uintptr_t)gate | (uintptr_t)out) & 15) == 0) {
+        const dim3 grid((nh * dv / 4 + 255) / 256, T_ < 65535 ? T_ : 65535);
+        PL_CUDA(launch_pdl(head_gate4_kernel<T>, grid, dim3(256), 0, stream, (const T*)o, D, (const T*)gate, ldg, (T*)out, T_, nh, dv));
+        return 0;
+    }
+    const long long n = (long long)T_ * nh * dv;
+    const long long blocks = (n + 255) / 256;
+    PL_CUDA(launch_pdl(head_gate_kernel<T>, dim3((unsigned)(blocks < 4096 ? blocks : 4096)), dim3(256), 0, stream, (const T*)o, D,
+                       (const T*)gate, ldg, (T*)out, n, nh, dv));
+    return 0;
+}
+
 PL_EXPORT int pl_head_gate(const void* o, int dtype, int T, int D, const void* gate, int ldg, void* out, int nh, int dv,
                            cudaStream_t stream) {
     if (T == 0) return 0;
     PL_REQUIRE(nh > 0 && dv > 0 && D >= dv, "head_gate: bad sizes dv=%d D=%d", dv, D);
-    const long long n = (long long)T * nh * dv;
-    const long long blocks = (n + 255) / 256;
-    const dim3 grid((unsigned)(blocks < 4096 ? blocks : 4096));
-    if (dtype == PL_F32)
-        PL_CUDA(launch_pdl(head_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)o, D, (const float*)gate, ldg,
-                           (float*)out, n, nh, dv));
-    else if (dtype == PL_BF16)
-        PL_CUDA(launch_pdl(head_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o, D,
-                           (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, n, nh, dv));
-    else
-        return pl_fail("head_gate: unknown dtype %d", dtype);
-    return 0;
+    if (dtype == PL_F32) return launch_head_gate<float>(o, T, D, gate, ldg, out, nh, dv, stream);
+    if (dtype == PL_BF16) return launch_head_gate<__nv_bfloat16>(o, T, D, gate, ldg, out, nh, dv, stream);
+    return pl_fail("head_gate: unknown dtype %d", dtype);
 }
 
 // ------------------------------------------------------------------ latent attention

@@ -543,7 +543,7 @@ class CudaOps:
         S = ctx.num_seqs
         _check(lib, lib.pl_ssm_conv(self._p(zx), self._code(zx), ld, inner, C, 2 * inner + 2 * G * N, H, self._p(conv_w),
                                     self._p(conv_b), taps, self._p(dt_bias), self._p(a_log), self._p(state),
-                                    c_longlong(state.shape[1]), self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S,
+                                    c_longlong(state.shape[1]), self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S, T,
                                     self._p(xbc), self._p(dt), self._p(decay), self._stream))
         _check(lib, lib.pl_ssm_scan(self._p(xbc), C, inner, G, N, H, P, self._p(dt), self._p(decay), self._p(d_skip),
                                     self._p(state), c_longlong(state.shape[1]), c_longlong((taps - 1) * C),

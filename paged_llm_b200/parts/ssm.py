@@ -65,6 +65,9 @@ class StateSpaceMixer(Mixer):
 
     def forward(self, h, ctx, cache):
         ops = ctx.ops
+        if any(slot < 0 for slot in ctx.host.state_slots):
+            raise RuntimeError("a request of a model with per-request state runs without a state slot "
+                               "(CacheManager.acquire_state_slot at its admission)")
         zx = ops.linear(h, self.w_in)
         y = ops.ssm_mix(zx, self.inner, self.groups, self.state_size, self.num_heads, self.head_dim, self.conv_w,
                         self.conv_b, self.dt_bias, self.a_log, self.d_skip, self.norm_w, self.norm_groups, self.eps,

@@ -65,10 +65,10 @@ def bucket(n: int, rows: int, far: float) -> int:
 def distance_bias(rel, T: int, far: float):
     """[heads, T, T]: rel[bucket(i - j), head] (zero where j > i; the mask removes those)."""
     rows, heads = rel.shape
-    idx = torch.zeros(T, T, dtype=torch.long)
-    for i in range(T):
-        for j in range(i + 1):
-            idx[i, j] = bucket(i - j, rows, far)
+    by_distance = torch.tensor([bucket(n, rows, far) for n in range(T)], dtype=torch.long)
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    idx = by_distance[(i - j).clamp(min=0)]
     return rel.to(F64)[idx].permute(2, 0, 1)
 
 
@@ -168,11 +168,11 @@ def selective_scan(x, dt, a_log, B, C, D, heads_per_group: int):
     S = torch.zeros(H, N, P, dtype=F64)
     y = torch.zeros(T, H, P, dtype=F64)
     A = torch.exp(a_log.to(F64))
+    group = torch.arange(H) // heads_per_group
     for t in range(T):
-        for hd in range(H):
-            g = hd // heads_per_group
-            S[hd] = math.exp(-A[hd] * dt[t, hd]) * S[hd] + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
-            y[t, hd] = S[hd].T @ C[t, g] + D[hd].to(F64) * x[t, hd]
+        Bt, Ct = B[t, group], C[t, group]                                    # [H, N]
+        S = torch.exp(-A * dt[t])[:, None, None] * S + dt[t][:, None, None] * Bt[:, :, None] * x[t][:, None, :]
+        y[t] = (S * Ct[:, :, None]).sum(1) + D.to(F64)[:, None] * x[t]
     return y
 
 
@@ -203,7 +203,7 @@ def dense_mlp(w, p, h):
 def forward(cfg: dict, w: dict, tokens, collect=None):
     """Logits [T, vocab] in float64.  `collect`, a list, receives the stream after every layer."""
     eps = cfg["norm"]["eps"]
-    x = w["embed"].to(F64)[torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = w["embed"].to(F64)[torch.as_tensor(tokens, dtype=torch.long)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     kept = {}
     for i, lay in enumerate(cfg["layers"]):
         pre, m = f"l{i}.", lay["mixer"]
@@ -223,3 +223,23 @@ def forward(cfg: dict, w: dict, tokens, collect=None):
         if collect is not None:
             collect.append(x.clone())
     return lin(w["head"], dyt(w, "final.norm", x))
+
+
+def attend(q, k, v, scale: float, window: int | None = None, bias_by_distance=None, first_position: int = 0):
+    """Attention of query rows q [nq, H, d] at positions first_position.. over keys k [L, G, d] and values
+    v [L, G, dv] at positions 0..L-1 (L = first_position + nq); `bias_by_distance` [H, n] is read at
+    min(distance, n - 1).  Returns [nq, H, dv] in float64."""
+    nq, H, _ = q.shape
+    L, G, _ = k.shape
+    kh = k.to(F64).repeat_interleave(H // G, dim=1)
+    vh = v.to(F64).repeat_interleave(H // G, dim=1)
+    pos = first_position + torch.arange(nq)
+    dist = pos[:, None] - torch.arange(L)[None, :]
+    scores = torch.einsum("qhd,khd->hqk", q.to(F64), kh) * scale
+    if bias_by_distance is not None:
+        scores = scores + bias_by_distance.to(F64)[:, dist.clamp(0, bias_by_distance.shape[1] - 1)]
+    hidden = dist < 0
+    if window is not None:
+        hidden |= dist >= window
+    a = torch.softmax(scores.masked_fill(hidden[None], float("-inf")), dim=-1)
+    return torch.einsum("hqk,khd->qhd", a, vh)
