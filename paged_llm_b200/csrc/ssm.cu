@@ -107,17 +107,17 @@ PL_EXPORT int pl_ssm_conv(const void* zx, int dtype, int ld, int c0, int C, int 
 }
 
 // ------------------------------------------------------------------ the recurrence
-// grid: (requests, heads, blocks of 16 columns).  A column p of a head's state is independent of the others:
-// eight lanes share it, each keeping NPER of its N values in registers, so a warp runs four columns and a block
-// of 128 threads sixteen.  The tokens' B, C, x, dt and decay come into shared memory sixteen tokens at a time by
+// grid: (requests, heads, blocks of columns).  A column p of a head's state is independent of the others:
+// eight or sixteen lanes share it, each keeping NPER of its N values in registers, and a block of 128 threads
+// runs sixteen or eight columns.  The tokens' B, C, x, dt and decay come into shared memory sixteen tokens at a time by
 // asynchronous copies, two chunks in flight: the copies of the next chunk run while this one is computed.  Per
 // token a lane does 2 NPER multiply-adds and keeps its part of the token's output; the parts of the sixteen
-// tokens are summed over the eight lanes together at the end of the chunk, so the only chain from token to token
+// tokens are summed over the lanes together at the end of the chunk, so the only chain from token to token
 // is the state's own multiply-add.
 // VEC (N, the row of xBC and the head size are multiples of four): 16-byte copies and reads; lane l holds the
-// values n = (8 j + l) * 4 + k, so that the eight lanes' reads of shared memory and of the state are contiguous.
+// values n = (lanes j + l) * 4 + k, so that the lanes' reads of shared memory and of the state are contiguous.
 // Otherwise 4-byte copies and n = l + 8 i.
-constexpr int SCAN_COLS = 16, SCAN_TOK = 16, SCAN_LANES = 8;
+constexpr int SCAN_TOK = 16;
 
 __device__ __forceinline__ void cp_async_f(float* dst, const float* src, bool ok) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
@@ -128,7 +128,7 @@ __device__ __forceinline__ void cp_async_f4(float* dst, const float* src, bool o
                  "r"(ok ? 16 : 0));
 }
 
-template <int NPER, bool VEC>
+template <int NPER, bool VEC, int SCAN_LANES>
 __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int G, int N, int H,
                                                        int P, const float* __restrict__ dt, const float* __restrict__ decay,
                                                        const float* __restrict__ Dskip, float* __restrict__ state,
@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__
                                                        const int* __restrict__ cu_q, const int* __restrict__ slots,
                                                        float* __restrict__ y) {
     extern __shared__ __align__(16) float sm[];
+    constexpr int SCAN_COLS = 128 / SCAN_LANES;                     // columns of a block
     constexpr int ROW = SCAN_LANES * NPER;                          // a token's B (or C), zeros from N on
     constexpr int STAGE = 2 * SCAN_TOK * ROW + SCAN_TOK * SCAN_COLS + 2 * SCAN_TOK;
     const int s = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * SCAN_COLS;
@@ -255,29 +256,28 @@ __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__
                 part[t] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             }
         }
-        // the eight lanes' parts of sixteen tokens: halve the tokens a lane is responsible for at every
-        // exchange (8, 4, 2), so that a lane ends with the sums of two tokens
+        // the lanes' parts of sixteen tokens: at every exchange a lane hands half of the tokens it is still
+        // responsible for to its partner and takes the partner's parts of the other half, so that after
+        // log2(lanes) exchanges it holds the full sums of 16 / lanes tokens, the first of which is token `tb`
+        int tb = 0;
+        {
+            int cnt = SCAN_TOK;
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-            const bool upper = lane & 4;
-            const float give = upper ? part[t] : part[t + 8], keep = upper ? part[t + 8] : part[t];
-            part[t] = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+            for (int m = SCAN_LANES / 2; m >= 1; m >>= 1) {
+                cnt >>= 1;
+                const bool upper = lane & m;
+#pragma unroll
+                for (int t = 0; t < SCAN_TOK / 2; ++t) {
+                    if (t < cnt) {
+                        const float give = upper ? part[t] : part[t + cnt], keep = upper ? part[t + cnt] : part[t];
+                        part[t] = keep + __shfl_xor_sync(0xffffffffu, give, m);
+                    }
+                }
+                tb += upper ? cnt : 0;
+            }
         }
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const bool upper = lane & 2;
-            const float give = upper ? part[t] : part[t + 4], keep = upper ? part[t + 4] : part[t];
-            part[t] = keep + __shfl_xor_sync(0xffffffffu, give, 2);
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const bool upper = lane & 1;
-            const float give = upper ? part[t] : part[t + 2], keep = upper ? part[t + 2] : part[t];
-            part[t] = keep + __shfl_xor_sync(0xffffffffu, give, 1);
-        }
-        const int tb = ((lane & 4) ? 8 : 0) + ((lane & 2) ? 4 : 0) + ((lane & 1) ? 2 : 0);
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
+        for (int e = 0; e < SCAN_TOK / SCAN_LANES; ++e) {
             const int t = tb + e;
             if (ok && t < nt)
                 y[(size_t)(q0 + t0 + t) * inner + (size_t)h * P + p] = fmaf(dskip, xs[t * SCAN_COLS + col], part[e]);
@@ -299,6 +299,185 @@ __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__
     }
 }
 
+// The same recurrence with the state values of FOUR columns per thread (N, the row of xBC and the state's
+// layout allow 16-byte accesses).  In the kernel above every column's lanes read all of B_t and C_t from shared
+// memory for two multiply-adds per value read, and shared memory, not the multiply-adds, sets the pace; here a
+// group of LPG lanes owns four columns, a lane keeps the values n = (LPG v + lane) * 4 + k (v < NV, k < 4) of all
+// four, and a 16-byte read of B_t and of C_t feeds 32 multiply-adds.  A block of 128 threads runs 512 / LPG
+// columns.  The 64 partial outputs of a chunk (16 tokens x 4 columns) are summed over the group's lanes together.
+template <int LPG, int NV>
+__global__ void __launch_bounds__(128) ssm_scan4_kernel(const float* __restrict__ xbc, int C, int inner, int G, int N, int H,
+                                                        int P, const float* __restrict__ dt, const float* __restrict__ decay,
+                                                        const float* __restrict__ Dskip, float* __restrict__ state,
+                                                        long long state_stride, long long ssm_off,
+                                                        const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                                        float* __restrict__ y) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int COLS = 512 / LPG;                                 // columns of a block
+    constexpr int ROW = LPG * NV * 4;                               // a token's B (or C), zeros from N on
+    constexpr int STAGE = 2 * SCAN_TOK * ROW + SCAN_TOK * COLS + 2 * SCAN_TOK;
+    const int s = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * COLS;
+    const int slot = slots[s];
+    const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
+    if (slot < 0 || nq <= 0) return;
+    const int g = h / (H / G);
+    const int tid = threadIdx.x, lane = tid & (LPG - 1), grp = tid / LPG;
+    const int pc = p0 + grp * 4;                                    // the group's first column
+    const float* b_src = xbc + inner + (size_t)g * N;
+    const float* c_src = xbc + inner + (size_t)G * N + (size_t)g * N;
+    const float* x_src = xbc + (size_t)h * P + p0;
+
+    auto issue = [&](int stage, int t0) {
+        float* Bs = sm + stage * STAGE;
+        float* Cs = Bs + SCAN_TOK * ROW;
+        float* xs = Cs + SCAN_TOK * ROW;
+        float* ds = xs + SCAN_TOK * COLS;
+        const int nt = min(SCAN_TOK, nq - t0);
+        // (tokens behind the chunk's last are never read: nothing is copied for them)
+#pragma unroll
+        for (int i = tid; i < SCAN_TOK * ROW / 4; i += 128) {
+            const int t = i / (ROW / 4), n = (i - t * (ROW / 4)) * 4;
+            if (t >= nt) break;
+            const bool in = n < N;
+            const size_t row = (size_t)(q0 + t0 + t) * C + (in ? n : 0);
+            cp_async_f4(Bs + t * ROW + n, b_src + row, in);
+            cp_async_f4(Cs + t * ROW + n, c_src + row, in);
+        }
+#pragma unroll
+        for (int i = tid; i < SCAN_TOK * COLS; i += 128) {
+            const int t = i / COLS, cc = i - t * COLS;
+            if (t >= nt) break;
+            const bool in = p0 + cc < P;
+            cp_async_f(xs + i, x_src + (size_t)(q0 + t0 + t) * C + (in ? cc : 0), in);
+        }
+        if (tid < 2 * SCAN_TOK) {
+            const int t = tid >> 1;
+            const bool in = t < nt;
+            cp_async_f(ds + tid, ((tid & 1) ? decay : dt) + (size_t)(q0 + t0 + (in ? t : 0)) * H + h, in);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    issue(0, 0);
+    float* sp = state + (size_t)slot * state_stride + ssm_off + (size_t)h * P * N;
+    float S[4][NV * 4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int n = (v * LPG + lane) * 4;
+            const float4 val = pc + c < P && n < N ? *reinterpret_cast<const float4*>(sp + (size_t)(pc + c) * N + n)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[c][4 * v] = val.x, S[c][4 * v + 1] = val.y, S[c][4 * v + 2] = val.z, S[c][4 * v + 3] = val.w;
+        }
+    const float dskip = __ldg(Dskip + h);
+    const int n_chunks = (nq + SCAN_TOK - 1) / SCAN_TOK;
+    for (int k = 0; k < n_chunks; ++k) {
+        const int t0 = k * SCAN_TOK;
+        const int nt = min(SCAN_TOK, nq - t0);
+        if (k + 1 < n_chunks) {
+            issue((k + 1) & 1, t0 + SCAN_TOK);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        const float* Bs = sm + (k & 1) * STAGE;
+        const float* Cs = Bs + SCAN_TOK * ROW;
+        const float* xs = Cs + SCAN_TOK * ROW;
+        const float* ds = xs + SCAN_TOK * COLS;
+        float part[SCAN_TOK * 4];                                   // [token][column]
+#pragma unroll
+        for (int t = 0; t < SCAN_TOK; ++t) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) part[4 * t + c] = 0.f;
+            if (t < nt) {                                           // (the state stays what the last real token left)
+                const float4 x4 = *reinterpret_cast<const float4*>(xs + t * COLS + grp * 4);
+                const float dtv = ds[2 * t], a = ds[2 * t + 1];
+                const float dtx[4] = {dtv * x4.x, dtv * x4.y, dtv * x4.z, dtv * x4.w};
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const int n = (v * LPG + lane) * 4;
+                    const float4 b = *reinterpret_cast<const float4*>(Bs + t * ROW + n);
+                    const float4 cc = *reinterpret_cast<const float4*>(Cs + t * ROW + n);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float* Sc = S[c] + 4 * v;
+                        Sc[0] = fmaf(a, Sc[0], dtx[c] * b.x);
+                        Sc[1] = fmaf(a, Sc[1], dtx[c] * b.y);
+                        Sc[2] = fmaf(a, Sc[2], dtx[c] * b.z);
+                        Sc[3] = fmaf(a, Sc[3], dtx[c] * b.w);
+                        part[4 * t + c] = fmaf(Sc[3], cc.w, fmaf(Sc[2], cc.z, fmaf(Sc[1], cc.y, fmaf(Sc[0], cc.x, part[4 * t + c]))));
+                    }
+                }
+            }
+        }
+        // the group's lanes' parts of 64 outputs: at every exchange a lane hands half of the outputs it is still
+        // responsible for to its partner and takes the partner's parts of the other half
+        int first = 0;
+        if (nt == 1) {
+            // one token (a decode step): the four outputs by a plain exchange over the group, every lane gets all
+#pragma unroll
+            for (int m = LPG / 2; m >= 1; m >>= 1)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], m);
+            if (lane < 4 && pc + lane < P) {
+                const float v = lane == 0 ? part[0] : lane == 1 ? part[1] : lane == 2 ? part[2] : part[3];
+                y[(size_t)(q0 + t0) * inner + (size_t)h * P + pc + lane] = fmaf(dskip, xs[grp * 4 + lane], v);
+            }
+        } else {
+            int cnt = SCAN_TOK * 4;
+#pragma unroll
+            for (int m = LPG / 2; m >= 1; m >>= 1) {
+                cnt >>= 1;
+                const bool upper = lane & m;
+#pragma unroll
+                for (int i = 0; i < SCAN_TOK * 2; ++i) {
+                    if (i < cnt) {
+                        const float give = upper ? part[i] : part[i + cnt], keep = upper ? part[i + cnt] : part[i];
+                        part[i] = keep + __shfl_xor_sync(0xffffffffu, give, m);
+                    }
+                }
+                first += upper ? cnt : 0;
+            }
+#pragma unroll
+            for (int e = 0; e < SCAN_TOK * 4 / LPG; ++e) {
+                const int o = first + e, t = o >> 2, c = o & 3;
+                if (pc + c < P && t < nt)
+                    y[(size_t)(q0 + t0 + t) * inner + (size_t)h * P + pc + c] = fmaf(dskip, xs[t * COLS + grp * 4 + c], part[e]);
+            }
+        }
+        __syncthreads();                                           // the stage is free for the chunk after next
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int n = (v * LPG + lane) * 4;
+            if (pc + c < P && n < N)
+                *reinterpret_cast<float4*>(sp + (size_t)(pc + c) * N + n) =
+                    make_float4(S[c][4 * v], S[c][4 * v + 1], S[c][4 * v + 2], S[c][4 * v + 3]);
+        }
+}
+
+template <int LPG, int NV>
+static int launch_scan4(const float* xbc, int C, int inner, int G, int N, int H, int P, const float* dt, const float* decay,
+                        const float* Dskip, float* state, long long state_stride, long long ssm_off, const int* cu_q,
+                        const int* slots, int num_seqs, float* y, cudaStream_t stream) {
+    constexpr int COLS = 512 / LPG;
+    const size_t smem = (size_t)2 * (2 * SCAN_TOK * LPG * NV * 4 + SCAN_TOK * COLS + 2 * SCAN_TOK) * sizeof(float);
+    auto kernel = ssm_scan4_kernel<LPG, NV>;
+    static bool attr_set = false;
+    if (smem > 48 * 1024 && !attr_set) {
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    kernel<<<dim3(num_seqs, H, (P + COLS - 1) / COLS), 128, smem, stream>>>(xbc, C, inner, G, N, H, P, dt, decay, Dskip, state,
+                                                                           state_stride, ssm_off, cu_q, slots, y);
+    PL_LAUNCHED("ssm_scan");
+    return 0;
+}
+
 PL_EXPORT int pl_ssm_scan(const float* xbc, int C, int inner, int G, int N, int H, int P, const float* dt,
                           const float* decay, const float* Dskip, float* state, long long state_stride, long long ssm_off,
                           const int* cu_q, const int* slots, int num_seqs, float* y, cudaStream_t stream) {
@@ -306,14 +485,27 @@ PL_EXPORT int pl_ssm_scan(const float* xbc, int C, int inner, int G, int N, int 
     PL_REQUIRE(G > 0 && H > 0 && H % G == 0 && N > 0 && P > 0 && inner == H * P && C == inner + 2 * G * N,
                "ssm_scan: bad sizes heads=%d groups=%d state=%d head size=%d", H, G, N, P);
     PL_REQUIRE(N <= 256, "ssm_scan: a state of %d values per column is more than the kernel keeps in registers (256)", N);
-    const dim3 grid(num_seqs, H, (P + SCAN_COLS - 1) / SCAN_COLS);
-    const int per = (N + SCAN_LANES - 1) / SCAN_LANES;
+    const bool vec4 = N % 4 == 0 && C % 4 == 0 && inner % 4 == 0 && P % 4 == 0 && state_stride % 4 == 0 && ssm_off % 4 == 0 &&
+                      (((uintptr_t)xbc | (uintptr_t)state) & 15) == 0;
+    if (vec4) {
+#define PL_SCAN4(L, V) return launch_scan4<L, V>(xbc, C, inner, G, N, H, P, dt, decay, Dskip, state, state_stride, ssm_off, cu_q, slots, num_seqs, y, stream)
+        if (N <= 16) PL_SCAN4(4, 1);
+        if (N <= 32) PL_SCAN4(8, 1);
+        if (N <= 64) PL_SCAN4(16, 1);
+        if (N <= 128) PL_SCAN4(32, 1);
+        PL_SCAN4(32, 2);
+#undef PL_SCAN4
+    }
+    // (sixteen lanes per column were tried for 64 state values and more: slower in prompts and in decoding)
+    const int lanes = 8;
+    const dim3 grid(num_seqs, H, (P + 128 / lanes - 1) / (128 / lanes));
+    const int per = (N + lanes - 1) / lanes;
     const bool vec = N % 4 == 0 && C % 4 == 0 && inner % 4 == 0 && state_stride % 4 == 0 && ssm_off % 4 == 0 &&
                      (((uintptr_t)xbc | (uintptr_t)state) & 15) == 0;
-#define PL_SCAN(NP, V)                                                                                                     \
+#define PL_SCAN(NP, V, L)                                                                                                  \
     do {                                                                                                                   \
-        const size_t smem = (size_t)2 * (2 * SCAN_TOK * SCAN_LANES * NP + SCAN_TOK * SCAN_COLS + 2 * SCAN_TOK) * sizeof(float); \
-        auto kernel = ssm_scan_kernel<NP, V>;                                                                              \
+        const size_t smem = (size_t)2 * (2 * SCAN_TOK * L * NP + SCAN_TOK * (128 / L) + 2 * SCAN_TOK) * sizeof(float);     \
+        auto kernel = ssm_scan_kernel<NP, V, L>;                                                                           \
         static bool attr_set = false;                                                                                      \
         if (smem > 48 * 1024 && !attr_set) {                                                                               \
             PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
@@ -322,17 +514,25 @@ PL_EXPORT int pl_ssm_scan(const float* xbc, int C, int inner, int G, int N, int 
         kernel<<<grid, 128, smem, stream>>>(xbc, C, inner, G, N, H, P, dt, decay, Dskip, state, state_stride, ssm_off, cu_q, \
                                             slots, y);                                                                     \
     } while (0)
-    if (vec) {
-        if (per <= 4) PL_SCAN(4, true);
-        else if (per <= 8) PL_SCAN(8, true);
-        else if (per <= 16) PL_SCAN(16, true);
-        else PL_SCAN(32, true);
+    if (lanes == 16) {
+        if (vec) {
+            if (per <= 4) PL_SCAN(4, true, 16);
+            else if (per <= 8) PL_SCAN(8, true, 16);
+            else PL_SCAN(16, true, 16);
+        } else {
+            if (per <= 4) PL_SCAN(4, false, 16);
+            else if (per <= 8) PL_SCAN(8, false, 16);
+            else PL_SCAN(16, false, 16);
+        }
     } else {
-        if (per <= 2) PL_SCAN(2, false);
-        else if (per <= 4) PL_SCAN(4, false);
-        else if (per <= 8) PL_SCAN(8, false);
-        else if (per <= 16) PL_SCAN(16, false);
-        else PL_SCAN(32, false);
+        if (vec && per > 2) {
+            if (per <= 4) PL_SCAN(4, true, 8);
+            else PL_SCAN(8, true, 8);
+        } else {
+            if (per <= 2) PL_SCAN(2, false, 8);
+            else if (per <= 4) PL_SCAN(4, false, 8);
+            else PL_SCAN(8, false, 8);
+        }
     }
 #undef PL_SCAN
     PL_LAUNCHED("ssm_scan");
