@@ -478,16 +478,21 @@ static int launch_scan4(const float* xbc, int C, int inner, int G, int N, int H,
     return 0;
 }
 
+// `max_tokens`: no request of the step brings more (the step's token count will do).
 PL_EXPORT int pl_ssm_scan(const float* xbc, int C, int inner, int G, int N, int H, int P, const float* dt,
                           const float* decay, const float* Dskip, float* state, long long state_stride, long long ssm_off,
-                          const int* cu_q, const int* slots, int num_seqs, float* y, cudaStream_t stream) {
+                          const int* cu_q, const int* slots, int num_seqs, int max_tokens, float* y, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     PL_REQUIRE(G > 0 && H > 0 && H % G == 0 && N > 0 && P > 0 && inner == H * P && C == inner + 2 * G * N,
                "ssm_scan: bad sizes heads=%d groups=%d state=%d head size=%d", H, G, N, P);
     PL_REQUIRE(N <= 256, "ssm_scan: a state of %d values per column is more than the kernel keeps in registers (256)", N);
     const bool vec4 = N % 4 == 0 && C % 4 == 0 && inner % 4 == 0 && P % 4 == 0 && state_stride % 4 == 0 && ssm_off % 4 == 0 &&
                       (((uintptr_t)xbc | (uintptr_t)state) & 15) == 0;
-    if (vec4) {
+    // Prompt portions: four columns per thread.  Steps of a token or two per request are bound by reading and
+    // writing the state, and the kernel with a column per eight lanes, which needs half the registers, keeps more
+    // of those accesses in flight (64 requests at 64 heads x 64 x 128: 56 against 85 us).
+    const bool few = max_tokens <= 2 * num_seqs;
+    if (vec4 && !few) {
 #define PL_SCAN4(L, V) return launch_scan4<L, V>(xbc, C, inner, G, N, H, P, dt, decay, Dskip, state, state_stride, ssm_off, cu_q, slots, num_seqs, y, stream)
         if (N <= 16) PL_SCAN4(4, 1);
         if (N <= 32) PL_SCAN4(8, 1);
@@ -514,25 +519,17 @@ PL_EXPORT int pl_ssm_scan(const float* xbc, int C, int inner, int G, int N, int 
         kernel<<<grid, 128, smem, stream>>>(xbc, C, inner, G, N, H, P, dt, decay, Dskip, state, state_stride, ssm_off, cu_q, \
                                             slots, y);                                                                     \
     } while (0)
-    if (lanes == 16) {
-        if (vec) {
-            if (per <= 4) PL_SCAN(4, true, 16);
-            else if (per <= 8) PL_SCAN(8, true, 16);
-            else PL_SCAN(16, true, 16);
-        } else {
-            if (per <= 4) PL_SCAN(4, false, 16);
-            else if (per <= 8) PL_SCAN(8, false, 16);
-            else PL_SCAN(16, false, 16);
-        }
+    if (vec && per > 2) {
+        if (per <= 4) PL_SCAN(4, true, 8);
+        else if (per <= 8) PL_SCAN(8, true, 8);
+        else if (per <= 16) PL_SCAN(16, true, 8);
+        else PL_SCAN(32, true, 8);
     } else {
-        if (vec && per > 2) {
-            if (per <= 4) PL_SCAN(4, true, 8);
-            else PL_SCAN(8, true, 8);
-        } else {
-            if (per <= 2) PL_SCAN(2, false, 8);
-            else if (per <= 4) PL_SCAN(4, false, 8);
-            else PL_SCAN(8, false, 8);
-        }
+        if (per <= 2) PL_SCAN(2, false, 8);
+        else if (per <= 4) PL_SCAN(4, false, 8);
+        else if (per <= 8) PL_SCAN(8, false, 8);
+        else if (per <= 16) PL_SCAN(16, false, 8);
+        else PL_SCAN(32, false, 8);
     }
 #undef PL_SCAN
     PL_LAUNCHED("ssm_scan");

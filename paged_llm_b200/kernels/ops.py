@@ -547,7 +547,7 @@ class CudaOps:
                                     self._p(xbc), self._p(dt), self._p(decay), self._stream))
         _check(lib, lib.pl_ssm_scan(self._p(xbc), C, inner, G, N, H, P, self._p(dt), self._p(decay), self._p(d_skip),
                                     self._p(state), c_longlong(state.shape[1]), c_longlong((taps - 1) * C),
-                                    self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S, self._p(y), self._stream))
+                                    self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), S, T, self._p(y), self._stream))
         out = torch.empty((T, inner), dtype=zx.dtype, device=dev)
         _check(lib, lib.pl_gated_group_norm(self._p(y), self._p(zx), self._code(zx), ld, self._p(norm_w), c_float(eps),
                                             self._p(out), T, inner, norm_groups, self._p(ctx.token_seq), self._stream))
