@@ -57,14 +57,47 @@ __global__ void __launch_bounds__(256) ssm_conv_kernel(const T* __restrict__ zx,
     if (ok) {
         const float bias = __ldg(cb + c);
         const T* col = zx + (size_t)q0 * ld + c0 + c;
-        for (int t = t_lo + lane_t; t < t_hi; t += TL) {
-            float acc = bias;
-            for (int k = 0; k < taps; ++k) {
-                const int src = t - hist + k;
-                const float v = src >= 0 ? to_float(col[(size_t)src * ld]) : st[(size_t)(hist + src) * C + c];
-                acc = fmaf(__ldg(cw + (size_t)c * taps + k), v, acc);
+        auto input = [&](int src) { return src >= 0 ? to_float(col[(size_t)src * ld]) : st[(size_t)(hist + src) * C + c]; };
+        if (taps <= 8 && CL == 32) {                 // (steps of a token or two per request: the plain loop below)
+            // a token lane walks a run of consecutive tokens and keeps the last taps-1 inputs and the channel's
+            // weights in registers: one load per output
+            constexpr int PER = CONV_TOK / TL;
+            const int ta = t_lo + lane_t * PER, tb = min(t_hi, ta + PER);
+            float w[8], win[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                w[k] = k < taps ? __ldg(cw + (size_t)c * taps + k) : 0.f;      // w[k] multiplies the input k - hist back
+                win[k] = 0.f;
             }
-            xbc[(size_t)(q0 + t) * C + c] = silu_f(acc);
+            if (ta < tb) {
+#pragma unroll
+                for (int k = 0; k < 7; ++k)
+                    if (k < hist) win[k] = input(ta - hist + k);                // the inputs in front of the run
+            }
+            for (int t = ta; t < tb; ++t) {
+                const float cur = to_float(col[(size_t)t * ld]);
+                float acc = bias;
+#pragma unroll
+                for (int k = 0; k < 7; ++k)
+                    if (k < hist) acc = fmaf(w[k], win[k], acc);
+                // the current token's weight is the last column
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (k == hist) acc = fmaf(w[k], cur, acc);
+                xbc[(size_t)(q0 + t) * C + c] = silu_f(acc);
+#pragma unroll
+                for (int k = 0; k < 7; ++k)
+                    if (k + 1 < hist) win[k] = win[k + 1];
+#pragma unroll
+                for (int k = 0; k < 7; ++k)
+                    if (k == hist - 1) win[k] = cur;
+            }
+        } else {
+            for (int t = t_lo + lane_t; t < t_hi; t += TL) {
+                float acc = bias;
+                for (int k = 0; k < taps; ++k) acc = fmaf(__ldg(cw + (size_t)c * taps + k), input(t - hist + k), acc);
+                xbc[(size_t)(q0 + t) * C + c] = silu_f(acc);
+            }
         }
     }
     if (blockIdx.z != 0) return;
@@ -574,6 +607,30 @@ __global__ void __launch_bounds__(512) gated_group_norm_kernel(const float* __re
     const float* yr = y + (size_t)t * inner + c0;
     const T* zr = z + (size_t)t * ldz + c0;
     float sq = 0.f;
+    if (VEC && part <= (int)blockDim.x * 16) {
+        // the gated row stays in registers between the sum of squares and the scaling: y and z are read once
+        float4 keep[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            keep[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < part) {
+                const float4 a = Quad<float>::load(yr + i), g = Quad<T>::load(zr + i);
+                keep[j] = make_float4(a.x * silu_f(g.x), a.y * silu_f(g.y), a.z * silu_f(g.z), a.w * silu_f(g.w));
+                sq += (keep[j].x * keep[j].x + keep[j].y * keep[j].y) + (keep[j].z * keep[j].z + keep[j].w * keep[j].w);
+            }
+        }
+        const float r = 1.0f / sqrtf(block_sum(sq, red) / (float)part + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < part) {
+                const float4 ww = Quad<float>::load(w + c0 + i);
+                Quad<T>::store(o + i, make_float4(keep[j].x * r * ww.x, keep[j].y * r * ww.y, keep[j].z * r * ww.z, keep[j].w * r * ww.w));
+            }
+        }
+        return;
+    }
     if (VEC) {
         for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
             const float4 a = Quad<float>::load(yr + i), g = Quad<T>::load(zr + i);

@@ -120,6 +120,9 @@ def pad16(n: int) -> int:
     return -(-n // 16) * 16
 
 
+MAX_HEAD_DIM = 256      # the largest build of the attention kernels
+
+
 @register_mixer("gated_attention")
 class GatedAttention(Mixer):
     """Grouped-query attention over the paged cache with four things the plain part does not have:
@@ -154,6 +157,8 @@ class GatedAttention(Mixer):
         self.distance_bias, self.bias_far, self.bias_rows = bool(distance_bias), float(bias_far), int(bias_rows)
         self.gate, self.shares_cache = bool(gate), bool(shares_cache)
         self.cache_dim = pad16(max(head_dim, value_dim))
+        if self.cache_dim > MAX_HEAD_DIM:
+            raise ValueError(f"head sizes {head_dim} / {value_dim}: the attention kernels take heads of at most {MAX_HEAD_DIM}")
         self.names = weights
         self.w_in = self.w_o = self.q_weight = self.k_weight = self.bias_by_distance = None
 

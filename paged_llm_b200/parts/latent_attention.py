@@ -23,7 +23,7 @@ from __future__ import annotations
 
 import torch
 
-from .attention import pad16
+from .attention import MAX_HEAD_DIM, pad16
 from .base import LazyLinear, Mixer, PagedKV, TensorSpec, register_mixer
 
 
@@ -42,6 +42,9 @@ class LatentAttention(Mixer):
         if position is not None and (position.pairing != "interleaved" or position.rotary_dim > rot_dim):
             raise ValueError("latent attention rotates pairs (2i, 2i+1) of at most rot_dim elements")
         self.cache_dim = pad16(kv_rank + rot_dim)
+        if self.cache_dim > MAX_HEAD_DIM:
+            raise ValueError(f"kv_rank + rot_dim = {kv_rank + rot_dim}: the latent is cached as one head, and the attention "
+                             f"kernels take heads of at most {MAX_HEAD_DIM}")
         self.names = weights
         self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.w_o = self.q_weight = self.c_weight = None
 
