@@ -223,3 +223,17 @@ def test_greedy_generation_through_the_engine(folders):
     for p, o in zip(prompts, outs):
         assert o.token_ids == plain_greedy(folders["A"], p, 12)
     assert eng.block_manager.num_free_state_slots == 3
+
+
+def test_generation_with_preemption_restarts_the_state(folders):
+    """So few pages that running requests are preempted: a request that comes back starts at position 0 with a
+    zeroed state slot and ends with the tokens of an undisturbed run."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    prompts = list(requests_for(CASE_B["vocab"], (30, 26, 21, 12), seed=70).values())
+    eng = LLMEngine(folders["B"], dtype="float32", device="cpu", ops=TorchOps(), block_size=8, num_gpu_blocks=11,
+                    max_model_len=88, max_num_batched_tokens=24, max_num_seqs=4)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16))
+    assert sum(o.num_preemptions for o in outs) > 0, "the pool was meant to run out"
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_greedy(folders["B"], p, 16)
+    assert eng.block_manager.num_free_state_slots == 4
