@@ -284,7 +284,7 @@ def test_state_space_mixer_alone(ops, dtype, H, P, N, G, taps, parts):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,d,dv,window,rows,far", [(4, 2, 16, 32, 24, 12, 50.0), (6, 1, 32, 16, None, 8, 30.0), (2, 2, 64, 64, 16, 32, 100.0),
-                                                         (3, 3, 24, 8, 7, 4, 9.0), (5, 5, 96, 96, 40, 32, 120.5), (2, 1, 10, 6, 11, 5, 7.0)])
+                                                         (3, 3, 24, 8, 7, 4, 9.0), (5, 5, 96, 96, 40, 32, 120.5), (2, 1, 10, 6, 11, 5, 7.0), (24, 1, 16, 16, 30, 8, 20.0)])
 def test_gated_attention_mixer_alone(ops, dtype, nh, nkv, d, dv, window, rows, far):
     from paged_llm_b200.parts.attention import GatedAttention
     W = 64
@@ -310,7 +310,7 @@ def test_gated_attention_mixer_alone(ops, dtype, nh, nkv, d, dv, window, rows, f
     (2, 24, 8, 16, 24, 40, 17, 4, None), (3, 16, 16, 24, 32, 48, 100, 16, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}),
     (4, 32, 32, 32, 64, 96, None, 32, {"factor": 8.0, "original": 64, "fast": 32.0, "slow": 1.0}), (1, 8, 2, 8, 16, 8, 9, 2, None),
     (5, 40, 16, 48, 40, 112, 32, 16, {"factor": 2.0, "original": 16, "fast": 8.0, "slow": 2.0}),
-    (3, 6, 6, 5, 10, 7, 20, 4, None)])
+    (3, 6, 6, 5, 10, 7, 20, 4, None), (20, 8, 8, 8, 16, 24, 12, 8, None)])
 def test_latent_attention_mixer_alone(ops, dtype, nh, d, r, dv, qr, kr, window, dims, scaling):
     from paged_llm_b200.parts.latent_attention import LatentAttention
     from paged_llm_b200.parts.rope import RotaryEncoding
